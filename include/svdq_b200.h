@@ -1,0 +1,138 @@
+/*
+ * svdq_b200 — C ABI of the B200 (sm_100a) SVDQuant W4A4 linear.
+ *
+ * Plain pointers and sizes only; no C++ or framework types cross this line.
+ * Every function returns an SVDQ_* status, never throws, never allocates
+ * unless stated, and (except the *_host calls and svdq_device_status) never
+ * synchronises: kernels are queued on the `stream` argument (a cudaStream_t
+ * passed as void*; NULL = the default stream).  The caller owns every buffer.
+ *
+ * Each entry point names the reference interface it stands in for, by that
+ * project's own paths.
+ */
+#ifndef SVDQ_B200_H_
+#define SVDQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of 16-bit (and, for the weight packer, 32-bit) tensors */
+enum { SVDQ_DTYPE_F16 = 0, SVDQ_DTYPE_BF16 = 1, SVDQ_DTYPE_F32 = 2 };
+
+/* status codes */
+enum {
+  SVDQ_OK = 0,
+  SVDQ_ERR_NULL = 1,      /* a required pointer is NULL */
+  SVDQ_ERR_SHAPE = 2,     /* a size breaks the op's contract (see each function) */
+  SVDQ_ERR_DTYPE = 3,
+  SVDQ_ERR_ALIGN = 4,     /* a pointer is not 16-byte aligned */
+  SVDQ_ERR_LAUNCH = 5,    /* the CUDA runtime refused a launch / descriptor */
+  SVDQ_ERR_DEVICE = 6,    /* a kernel gave up on a bounded wait; see svdq_device_status */
+  SVDQ_ERR_UNSUPPORTED = 7,
+  SVDQ_ERR_CUDA = 8       /* other CUDA runtime failure (copy, allocation in plan/host calls) */
+};
+
+/* flags for svdq_quantize_w4a4_act_fuse_lora */
+enum {
+  SVDQ_QUANT_AUTO = 0,        /* fused tensor-core kernel when the shape allows, else the generic kernels */
+  SVDQ_QUANT_FORCE_GENERIC = 1,
+  SVDQ_QUANT_FORCE_FUSED = 2  /* error instead of falling back */
+};
+
+const char* svdq_status_string(int status);
+int svdq_version(void);
+
+/*
+ * Fused activation quantizer + LoRA-down.
+ * Stands in for quantize_w4a4_act_fuse_lora(input, lora_down, smooth, fp4=True, pad_size)
+ *   (triton_kernels/quantize_w4a4_act_fuse_lora/kernel.py:289-400; oracle
+ *    baseline/kernels/quantize_w4a4_act_fuse_lora/ref.py:19-50).
+ *
+ *   x          [M, K]        f16/bf16, row-major, K % 16 == 0
+ *   lora_down  [K, R]        same type (R may be 0, then lora_down may be NULL)
+ *   smooth     [K] or NULL   same type
+ *   act        [M_pad, K/2]  u8   two E2M1 codes per byte, even k in the low nibble
+ *   ascales    [K/16, M_pad] u8   E4M3 bit patterns (the reference's transposed layout)
+ *   lora_act   [M_pad, R]    f32  rows >= M are zero
+ *   ascales_swz  optional, M_pad*K/16 bytes: the same scales in the 128-row x 4-group
+ *                atom order the tensor core reads (needs M_pad % 128 == 0, K % 64 == 0)
+ *   lora_act16   optional [M_pad, R] in x's type: lora_act rounded once to 16 bit
+ *   M_pad      rows of the outputs, >= M (the reference pads M up to a multiple of 256)
+ * Rows M..M_pad-1 of act / ascales are written as zero bytes, as the oracle does.
+ */
+int svdq_quantize_w4a4_act_fuse_lora(const void* x, const void* lora_down, const void* smooth,
+                                     void* act, void* ascales, float* lora_act,
+                                     void* ascales_swz, void* lora_act16,
+                                     int M, int K, int R, int M_pad, int dtype, int flags, void* stream);
+
+/*
+ * NVFP4 row packer (weights: pad 1).
+ * Stands in for quantize_nvfp4_rows(x, pad_size) (baseline/kernels/_nvfp4.py:60-95).
+ *   x [rows, K] f16/bf16/f32 -> codes [rows_pad, K/2], scales [K/16, rows_pad],
+ *   optional scales_swz as above.
+ */
+int svdq_quantize_nvfp4_rows(const void* x, void* codes, void* scales, void* scales_swz,
+                             int rows, int rows_pad, int K, int dtype, void* stream);
+
+/*
+ * Canonical [K/16, rows] scale bytes -> tensor-core atom order.
+ * Stands in for _repack_scales_cutlass_atom (cute_kernels/gemm_w4a4/kernel.py:194-225).
+ * rows % 128 == 0 and (K/16) % 4 == 0.
+ */
+int svdq_swizzle_scales(const void* scales, void* scales_swz, int k_groups, int rows, void* stream);
+
+/* f32 -> f16/bf16 copy of lora_act (the cast launch_v2 does at
+ * cute_kernels/gemm_w4a4/kernel_v2_fa4.py:176-184). */
+int svdq_cast_lora_act(const float* src, void* dst, long long count, int dtype, void* stream);
+
+/*
+ * W4A4 GEMM + LoRA-up + per-column affine.
+ * Stands in for launch_v2(act, wgt, ascales, wscales, lora_act_in, lora_up, wcscales, bias, out_dtype)
+ *   (cute_kernels/gemm_w4a4/kernel_v2_fa4.py:113-225; oracle baseline/kernels/gemm_w4a4/ref.py:33-78).
+ *
+ *   act         [M, K/2] u8        wgt        [N, K/2] u8
+ *   ascales_swz  M*K/16 bytes      wscales_swz N*K/16 bytes   (atom order, see above)
+ *   lora_act16  [M, R] f16/bf16 or NULL      lora_up [N, R] same type or NULL (both or neither)
+ *   wcscales    [N] or NULL        bias       [N] or NULL     (type = dtype)
+ *   y           [M, N] dtype
+ * Contract: M % 128 == 0, N % 128 == 0, K % 64 == 0, R % 16 == 0 (svdq_gemm_w4a4_supported).
+ * variant: 0 = pick the N tile (256 when N % 256 == 0, else 128); 128 / 256 = force it.
+ *   y = cast( (deq(act) deq(wgt)^T + lora_act16 lora_up^T) * wcscales + bias )
+ */
+int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                   const void* lora_act16, const void* lora_up, const void* wcscales, const void* bias,
+                   void* y, int M, int N, int K, int R, int dtype, int variant, void* stream);
+
+/* 1 if (M, N, K, R) is inside the GEMM contract, else 0. */
+int svdq_gemm_w4a4_supported(int M, int N, int K, int R);
+
+/*
+ * Reads (and clears) the device status word that kernels write when a bounded
+ * wait expires.  Synchronises the device.  out[0]=code (0 = clean), out[1]=block,
+ * out[2]=tag, out[3]=how many waits gave up.
+ */
+int svdq_device_status(unsigned int out[4]);
+
+/*
+ * Whole linear from HOST buffers: copies x to the device, runs quantizer and
+ * GEMM on weights already resident in the plan, copies y back and waits.
+ * A plan owns its device buffers (allocated once in svdq_linear_plan_create).
+ * There is no counterpart in the reference, whose ops take device tensors; this
+ * is the host-buffer form of calling its two ops back to back.
+ */
+typedef struct svdq_linear_plan svdq_linear_plan;
+int svdq_linear_plan_create(svdq_linear_plan** plan, int max_M, int K, int N, int R, int dtype,
+                            const void* wgt_host, const void* wscales_host, const void* lora_down_host,
+                            const void* lora_up_host, const void* smooth_host, const void* wcscales_host,
+                            const void* bias_host);
+int svdq_linear_plan_forward_host(svdq_linear_plan* plan, const void* x_host, void* y_host, int M);
+void svdq_linear_plan_destroy(svdq_linear_plan* plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SVDQ_B200_H_ */

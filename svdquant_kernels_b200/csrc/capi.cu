@@ -1,0 +1,229 @@
+// extern "C" surface of libsvdq_b200.so (declared in include/svdq_b200.h):
+// argument validation, dispatch between the fused and the generic quantizer,
+// the device status word, and the host-buffer "plan" used for end-to-end runs.
+#include <cstring>
+#include <new>
+
+#include "sm100.cuh"
+#include "svdq_internal.h"
+
+namespace svdq {
+
+int read_and_clear_status(unsigned int out[4]) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return SVDQ_ERR_CUDA;
+  if (cudaMemcpyFromSymbol(out, g_status_word, sizeof(unsigned int) * 4) != cudaSuccess) return SVDQ_ERR_CUDA;
+  if (out[0] != 0 || out[3] != 0) {
+    const unsigned int zero[4] = {0, 0, 0, 0};
+    if (cudaMemcpyToSymbol(g_status_word, zero, sizeof(zero)) != cudaSuccess) return SVDQ_ERR_CUDA;
+  }
+  return out[0] == 0 ? SVDQ_OK : SVDQ_ERR_DEVICE;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace svdq
+
+using namespace svdq;
+
+extern "C" {
+
+const char* svdq_status_string(int status) {
+  switch (status) {
+    case SVDQ_OK: return "ok";
+    case SVDQ_ERR_NULL: return "a required pointer is NULL";
+    case SVDQ_ERR_SHAPE: return "size outside the operator's contract";
+    case SVDQ_ERR_DTYPE: return "unsupported element type";
+    case SVDQ_ERR_ALIGN: return "pointer not 16-byte aligned";
+    case SVDQ_ERR_LAUNCH: return "CUDA launch or descriptor creation failed";
+    case SVDQ_ERR_DEVICE: return "a kernel gave up on a bounded wait";
+    case SVDQ_ERR_UNSUPPORTED: return "shape not supported by the requested kernel";
+    case SVDQ_ERR_CUDA: return "CUDA runtime call failed";
+    default: return "unknown status";
+  }
+}
+
+int svdq_version(void) { return 100; }
+
+int svdq_quantize_w4a4_act_fuse_lora(const void* x, const void* lora_down, const void* smooth, void* act,
+                                     void* ascales, float* lora_act, void* ascales_swz, void* lora_act16, int M,
+                                     int K, int R, int M_pad, int dtype, int flags, void* stream) {
+  if (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16) return SVDQ_ERR_DTYPE;
+  if (M < 0 || K <= 0 || R < 0 || M_pad < M || K % 16 != 0) return SVDQ_ERR_SHAPE;
+  if (M_pad == 0) return SVDQ_OK;
+  if (act == nullptr || ascales == nullptr || (M > 0 && x == nullptr)) return SVDQ_ERR_NULL;
+  if (R > 0 && (lora_down == nullptr || lora_act == nullptr)) return SVDQ_ERR_NULL;
+  if (!aligned16(x) || !aligned16(act) || !aligned16(smooth) || !aligned16(lora_down) || !aligned16(lora_act) ||
+      !aligned16(ascales_swz) || !aligned16(lora_act16))
+    return SVDQ_ERR_ALIGN;
+  if (ascales_swz != nullptr && (M_pad % 128 != 0 || K % 64 != 0)) return SVDQ_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool fused_ok = M > 0 && quantize_fused_supported(M, K, R, M_pad);
+  if (flags == SVDQ_QUANT_FORCE_FUSED && !fused_ok) return SVDQ_ERR_UNSUPPORTED;
+  if (fused_ok && flags != SVDQ_QUANT_FORCE_GENERIC)
+    return launch_quantize_fused(x, lora_down, smooth, act, ascales, lora_act, ascales_swz, lora_act16, M, K, R, M_pad,
+                                 dtype, st);
+  int rc = launch_quantize_rows(x, smooth, act, ascales, ascales_swz, M, M_pad, K, dtype, st);
+  if (rc != SVDQ_OK) return rc;
+  return launch_lora_down(x, lora_down, lora_act, lora_act16, M, M_pad, K, R, dtype, st);
+}
+
+int svdq_quantize_nvfp4_rows(const void* x, void* codes, void* scales, void* scales_swz, int rows, int rows_pad, int K,
+                             int dtype, void* stream) {
+  if (rows < 0 || rows_pad < rows || K <= 0 || K % 16 != 0) return SVDQ_ERR_SHAPE;
+  if (rows_pad == 0) return SVDQ_OK;
+  if (codes == nullptr || scales == nullptr || (rows > 0 && x == nullptr)) return SVDQ_ERR_NULL;
+  if (!aligned16(x) || !aligned16(codes) || !aligned16(scales_swz)) return SVDQ_ERR_ALIGN;
+  if (scales_swz != nullptr && (rows_pad % 128 != 0 || K % 64 != 0)) return SVDQ_ERR_SHAPE;
+  return launch_quantize_rows(x, nullptr, codes, scales, scales_swz, rows, rows_pad, K, dtype,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int svdq_swizzle_scales(const void* scales, void* scales_swz, int k_groups, int rows, void* stream) {
+  if (k_groups < 0 || rows < 0 || rows % 128 != 0 || k_groups % 4 != 0) return SVDQ_ERR_SHAPE;
+  if (k_groups == 0 || rows == 0) return SVDQ_OK;
+  if (scales == nullptr || scales_swz == nullptr) return SVDQ_ERR_NULL;
+  return launch_swizzle_scales(scales, scales_swz, k_groups, rows, static_cast<cudaStream_t>(stream));
+}
+
+int svdq_cast_lora_act(const float* src, void* dst, long long count, int dtype, void* stream) {
+  if (count < 0) return SVDQ_ERR_SHAPE;
+  if (count == 0) return SVDQ_OK;
+  if (src == nullptr || dst == nullptr) return SVDQ_ERR_NULL;
+  return launch_cast_f32(src, dst, count, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int svdq_gemm_w4a4_supported(int M, int N, int K, int R) { return gemm_supported(M, N, K, R) ? 1 : 0; }
+
+int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                   const void* lora_act16, const void* lora_up, const void* wcscales, const void* bias, void* y, int M,
+                   int N, int K, int R, int dtype, int variant, void* stream) {
+  if (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16) return SVDQ_ERR_DTYPE;
+  if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
+  if (act == nullptr || wgt == nullptr || ascales_swz == nullptr || wscales_swz == nullptr || y == nullptr)
+    return SVDQ_ERR_NULL;
+  if ((lora_act16 == nullptr) != (lora_up == nullptr)) return SVDQ_ERR_NULL;
+  if (R > 0 && lora_act16 == nullptr) return SVDQ_ERR_NULL;
+  if (lora_act16 == nullptr) R = 0;
+  if (!aligned16(act) || !aligned16(wgt) || !aligned16(ascales_swz) || !aligned16(wscales_swz) ||
+      !aligned16(lora_act16) || !aligned16(lora_up) || !aligned16(y))
+    return SVDQ_ERR_ALIGN;
+  return launch_gemm_w4a4(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, wcscales, bias, y, M, N, K, R, dtype,
+                          variant, static_cast<cudaStream_t>(stream));
+}
+
+int svdq_device_status(unsigned int out[4]) {
+  unsigned int tmp[4] = {0, 0, 0, 0};
+  int rc = read_and_clear_status(tmp);
+  if (out != nullptr)
+    for (int i = 0; i < 4; ++i) out[i] = tmp[i];
+  return rc;
+}
+
+// ---------------------------------------------------------------------------
+// host-buffer plan
+// ---------------------------------------------------------------------------
+struct svdq_linear_plan {
+  int max_M, max_M_pad, K, N, R, dtype;
+  cudaStream_t stream;
+  void *x, *act, *ascales, *ascales_swz, *lora_act16, *y;       // per-call device buffers
+  float* lora_act;
+  void *wgt, *wscales_swz, *lora_down, *lora_up, *smooth, *wc, *bias;  // resident weights
+  void *x_pin, *y_pin;                                           // pinned staging
+};
+
+static bool is_pinned_host(const void* ptr) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, ptr) != cudaSuccess) { cudaGetLastError(); return false; }
+  return a.type == cudaMemoryTypeHost;
+}
+
+static int dev_upload(void** dst, const void* src, size_t bytes, cudaStream_t st) {
+  *dst = nullptr;
+  if (src == nullptr || bytes == 0) return SVDQ_OK;
+  if (cudaMalloc(dst, bytes) != cudaSuccess) return SVDQ_ERR_CUDA;
+  if (cudaMemcpyAsync(*dst, src, bytes, cudaMemcpyHostToDevice, st) != cudaSuccess) return SVDQ_ERR_CUDA;
+  return SVDQ_OK;
+}
+
+int svdq_linear_plan_create(svdq_linear_plan** out, int max_M, int K, int N, int R, int dtype, const void* wgt_host,
+                            const void* wscales_host, const void* lora_down_host, const void* lora_up_host,
+                            const void* smooth_host, const void* wcscales_host, const void* bias_host) {
+  if (out == nullptr || wgt_host == nullptr || wscales_host == nullptr) return SVDQ_ERR_NULL;
+  if (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16) return SVDQ_ERR_DTYPE;
+  const int max_M_pad = (max_M + 255) / 256 * 256;
+  if (max_M <= 0 || !gemm_supported(max_M_pad, N, K, R)) return SVDQ_ERR_SHAPE;
+  if (R > 0 && (lora_down_host == nullptr || lora_up_host == nullptr)) return SVDQ_ERR_NULL;
+  svdq_linear_plan* p = new (std::nothrow) svdq_linear_plan();
+  if (p == nullptr) return SVDQ_ERR_CUDA;
+  p->max_M = max_M; p->max_M_pad = max_M_pad; p->K = K; p->N = N; p->R = R; p->dtype = dtype;
+  int rc = SVDQ_OK;
+  bool bad = cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking) != cudaSuccess;
+  const size_t mp = static_cast<size_t>(max_M_pad);
+  bad = bad || cudaMalloc(&p->x, static_cast<size_t>(max_M) * K * 2) != cudaSuccess;
+  bad = bad || cudaMalloc(&p->act, mp * K / 2) != cudaSuccess;
+  bad = bad || cudaMalloc(&p->ascales, mp * K / 16) != cudaSuccess;
+  bad = bad || cudaMalloc(&p->ascales_swz, mp * K / 16) != cudaSuccess;
+  bad = bad || cudaMalloc(&p->lora_act, mp * (R > 0 ? R : 1) * 4) != cudaSuccess;
+  bad = bad || cudaMalloc(&p->lora_act16, mp * (R > 0 ? R : 1) * 2) != cudaSuccess;
+  bad = bad || cudaMalloc(&p->y, mp * N * 2) != cudaSuccess;
+  bad = bad || cudaMallocHost(&p->x_pin, static_cast<size_t>(max_M) * K * 2) != cudaSuccess;
+  bad = bad || cudaMallocHost(&p->y_pin, mp * N * 2) != cudaSuccess;
+  if (bad) rc = SVDQ_ERR_CUDA;
+  void* wscales_dev = nullptr;
+  if (rc == SVDQ_OK) rc = dev_upload(&p->wgt, wgt_host, static_cast<size_t>(N) * K / 2, p->stream);
+  if (rc == SVDQ_OK) rc = dev_upload(&wscales_dev, wscales_host, static_cast<size_t>(N) * K / 16, p->stream);
+  if (rc == SVDQ_OK && cudaMalloc(&p->wscales_swz, static_cast<size_t>(N) * K / 16) != cudaSuccess) rc = SVDQ_ERR_CUDA;
+  if (rc == SVDQ_OK) rc = launch_swizzle_scales(wscales_dev, p->wscales_swz, K / 16, N, p->stream);
+  if (rc == SVDQ_OK) rc = dev_upload(&p->lora_down, lora_down_host, static_cast<size_t>(K) * R * 2, p->stream);
+  if (rc == SVDQ_OK) rc = dev_upload(&p->lora_up, lora_up_host, static_cast<size_t>(N) * R * 2, p->stream);
+  if (rc == SVDQ_OK) rc = dev_upload(&p->smooth, smooth_host, static_cast<size_t>(K) * 2, p->stream);
+  if (rc == SVDQ_OK) rc = dev_upload(&p->wc, wcscales_host, static_cast<size_t>(N) * 2, p->stream);
+  if (rc == SVDQ_OK) rc = dev_upload(&p->bias, bias_host, static_cast<size_t>(N) * 2, p->stream);
+  if (rc == SVDQ_OK && cudaStreamSynchronize(p->stream) != cudaSuccess) rc = SVDQ_ERR_CUDA;
+  if (wscales_dev != nullptr) cudaFree(wscales_dev);
+  if (rc != SVDQ_OK) {
+    svdq_linear_plan_destroy(p);
+    return rc;
+  }
+  *out = p;
+  return SVDQ_OK;
+}
+
+int svdq_linear_plan_forward_host(svdq_linear_plan* p, const void* x_host, void* y_host, int M) {
+  if (p == nullptr || x_host == nullptr || y_host == nullptr) return SVDQ_ERR_NULL;
+  if (M <= 0 || M > p->max_M) return SVDQ_ERR_SHAPE;
+  const int M_pad = (M + 255) / 256 * 256;
+  const size_t xbytes = static_cast<size_t>(M) * p->K * 2, ybytes = static_cast<size_t>(M) * p->N * 2;
+  // page-locked caller buffers are copied from directly; pageable ones go through the plan's pinned staging
+  const bool x_pinned = is_pinned_host(x_host), y_pinned = is_pinned_host(y_host);
+  const void* x_src = x_host;
+  if (!x_pinned) { memcpy(p->x_pin, x_host, xbytes); x_src = p->x_pin; }
+  if (cudaMemcpyAsync(p->x, x_src, xbytes, cudaMemcpyHostToDevice, p->stream) != cudaSuccess) return SVDQ_ERR_CUDA;
+  int rc = svdq_quantize_w4a4_act_fuse_lora(p->x, p->lora_down, p->smooth, p->act, p->ascales, p->lora_act,
+                                            p->ascales_swz, p->lora_act16, M, p->K, p->R, M_pad, p->dtype,
+                                            SVDQ_QUANT_AUTO, p->stream);
+  if (rc != SVDQ_OK) return rc;
+  rc = svdq_gemm_w4a4(p->act, p->wgt, p->ascales_swz, p->wscales_swz, p->R > 0 ? p->lora_act16 : nullptr,
+                      p->R > 0 ? p->lora_up : nullptr, p->wc, p->bias, p->y, M_pad, p->N, p->K, p->R, p->dtype, 0,
+                      p->stream);
+  if (rc != SVDQ_OK) return rc;
+  void* y_dst = y_pinned ? y_host : p->y_pin;
+  if (cudaMemcpyAsync(y_dst, p->y, ybytes, cudaMemcpyDeviceToHost, p->stream) != cudaSuccess) return SVDQ_ERR_CUDA;
+  if (cudaStreamSynchronize(p->stream) != cudaSuccess) return SVDQ_ERR_CUDA;
+  if (!y_pinned) memcpy(y_host, p->y_pin, ybytes);
+  return SVDQ_OK;
+}
+
+void svdq_linear_plan_destroy(svdq_linear_plan* p) {
+  if (p == nullptr) return;
+  void* dev[] = {p->x, p->act, p->ascales, p->ascales_swz, p->lora_act, p->lora_act16, p->y, p->wgt,
+                 p->wscales_swz, p->lora_down, p->lora_up, p->smooth, p->wc, p->bias};
+  for (void* d : dev)
+    if (d != nullptr) cudaFree(d);
+  if (p->x_pin != nullptr) cudaFreeHost(p->x_pin);
+  if (p->y_pin != nullptr) cudaFreeHost(p->y_pin);
+  if (p->stream != nullptr) cudaStreamDestroy(p->stream);
+  delete p;
+}
+
+}  // extern "C"

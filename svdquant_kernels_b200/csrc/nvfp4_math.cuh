@@ -1,0 +1,80 @@
+// Scalar NVFP4 arithmetic shared by the quantizer kernels.
+//
+// The rules restate baseline/kernels/_nvfp4.py:27-41 and :82-91 of the
+// reference so that codes and scales come out bit-identical:
+//   scale  = e4m3( clamp(amax / 6, 1e-12, 448) )        (IEEE fp32 divide, RNE cast)
+//   q      = v / float(scale)                           (IEEE fp32 divide)
+//   code   = #{ bounds b in {.25,.75,1.25,1.75,2.5,3.5,5} : |q| >= b }  |  (q < 0) << 3
+//
+// The per-element divide by the scale is never executed.  With s an e4m3 value
+// (4 significant bits) and b a bound (3 significant bits) the product s*b is
+// exact in fp32, and RN(|v| / s) >= b holds exactly when |v| >= s*b: the
+// quotients that round up to b from below would need |v| strictly between two
+// adjacent fp32 numbers.  So each group compares |v| with seven exact products.
+// A zero scale (amax/6 below 2^-10) makes every non-zero v an infinity (code 7)
+// and every zero a NaN (code 0); the smallest denormal as bound reproduces that.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace svdq {
+
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(float v) { return v; }
+
+// e4m3 byte of clamp(amax/6, 1e-12, 448); round-to-nearest-even incl. subnormals.
+__device__ __forceinline__ uint8_t scale_byte_from_amax(float amax) {
+  float s = __fdiv_rn(amax, 6.0f);
+  s = fminf(fmaxf(s, 1e-12f), 448.0f);
+  return static_cast<uint8_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3));
+}
+
+// exact value of a non-negative e4m3 byte
+__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
+  uint32_t e = (b >> 3) & 0xF, m = b & 7;
+  if (e == 0) return static_cast<float>(m) * 0.001953125f;  // m * 2^-9
+  return __uint_as_float(((e + 120u) << 23) | (m << 20));
+}
+
+struct GroupBounds {
+  float p[7];
+};
+
+__device__ __forceinline__ GroupBounds bounds_for_scale(float s) {
+  GroupBounds g;
+  if (s == 0.0f) {
+    const float tiny = __uint_as_float(1u);  // any non-zero magnitude saturates
+#pragma unroll
+    for (int i = 0; i < 7; ++i) g.p[i] = tiny;
+  } else {
+    g.p[0] = s * 0.25f; g.p[1] = s * 0.75f; g.p[2] = s * 1.25f; g.p[3] = s * 1.75f;
+    g.p[4] = s * 2.5f;  g.p[5] = s * 3.5f;  g.p[6] = s * 5.0f;
+  }
+  return g;
+}
+
+// 4-bit code of one value: three dependent compares instead of seven.
+__device__ __forceinline__ uint32_t e2m1_code(float v, const GroupBounds& g) {
+  const float a = fabsf(v);
+  const bool c4 = a >= g.p[3];
+  const float mid = c4 ? g.p[5] : g.p[1];
+  const bool c2 = a >= mid;
+  const float hi = c2 ? g.p[6] : g.p[4];
+  const float lo = c2 ? g.p[2] : g.p[0];
+  const bool c1 = a >= (c4 ? hi : lo);
+  uint32_t idx = (c4 ? 4u : 0u) + (c2 ? 2u : 0u) + (c1 ? 1u : 0u);
+  return idx | ((v < 0.0f) ? 8u : 0u);
+}
+
+// byte offset of (row m, group g) inside the 128-row x 4-group scale atoms the
+// tensor core reads (cute_kernels/gemm_w4a4/kernel.py:194-225 builds the same
+// order with a transpose + permute): atoms of 512 bytes ordered (m/128, g/4).
+__host__ __device__ __forceinline__ size_t sf_swizzled_offset(uint32_t m, uint32_t g, uint32_t groups) {
+  return (static_cast<size_t>(m >> 7) * (groups >> 2) + (g >> 2)) * 512u + (m & 31u) * 16u + ((m >> 5) & 3u) * 4u + (g & 3u);
+}
+
+}  // namespace svdq

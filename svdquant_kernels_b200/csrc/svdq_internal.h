@@ -1,0 +1,42 @@
+// Internal launch prototypes shared by the translation units of libsvdq_b200.so.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/svdq_b200.h"
+
+namespace svdq {
+
+// quantize_generic.cu
+int launch_quantize_rows(const void* x, const void* smooth, void* codes, void* scales, void* scales_swz, int rows,
+                         int rows_pad, int K, int dtype, cudaStream_t stream);
+int launch_lora_down(const void* x, const void* w, float* out, void* out16, int M, int M_pad, int K, int R, int dtype,
+                     cudaStream_t stream);
+int launch_swizzle_scales(const void* src, void* dst, int groups, int rows, cudaStream_t stream);
+int launch_cast_f32(const float* src, void* dst, long long n, int dtype, cudaStream_t stream);
+
+// quantize_fused.cu
+bool quantize_fused_supported(int M, int K, int R, int M_pad);
+int launch_quantize_fused(const void* x, const void* lora_down, const void* smooth, void* act, void* ascales,
+                          float* lora_act, void* ascales_swz, void* lora_act16, int M, int K, int R, int M_pad,
+                          int dtype, cudaStream_t stream);
+
+// gemm_w4a4.cu
+bool gemm_supported(int M, int N, int K, int R);
+int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                     const void* lora_act16, const void* lora_up, const void* wcscales, const void* bias, void* y,
+                     int M, int N, int K, int R, int dtype, int variant, cudaStream_t stream);
+
+// tensormap.cu : cuTensorMapEncodeTiled resolved through the runtime at first use
+enum TmapSwizzle { kTmapSwizzleNone = 0, kTmapSwizzle128 = 1 };
+// 2-D row-major tensor [rows, cols] of `elem_bytes`-sized elements; box = [box_rows, box_cols].
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                 uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols, TmapSwizzle swz);
+int sm_count();
+
+// status word (defined once in gemm_w4a4.cu via sm100.cuh's extern declaration)
+int read_and_clear_status(unsigned int out[4]);
+
+}  // namespace svdq

@@ -1,0 +1,289 @@
+"""Operator API of the W4A4 linear, drop-in for the reference's two entry points.
+
+    quantize_w4a4_act_fuse_lora(input, lora_down, smooth, *, fp4=True, pad_size=256)
+        -> (act u8 [M_pad, K/2], ascales e4m3 [K/16, M_pad], lora_act f32 [M_pad, R])
+        mirrors triton_kernels/quantize_w4a4_act_fuse_lora/kernel.py:289-400
+    gemm_w4a4(act, wgt, ascales, wscales, lora_act_in, lora_up, wcscales, bias, out_dtype=...)
+        -> y [M_pad, N]
+        mirrors launch_v2 at cute_kernels/gemm_w4a4/kernel_v2_fa4.py:113-225
+        (same argument meaning, AssertionError on contract violations as
+        cute_kernels/gemm_w4a4/kernel.py:116-171 raises them)
+    quantize_nvfp4_rows(x, pad_size=1) -> (packed, scales)
+        mirrors baseline/kernels/_nvfp4.py:60-95 (the offline weight packer), on the GPU
+
+Tensors stay torch tensors on the CUDA device; all arithmetic happens in
+libsvdq_b200.so through its C ABI on torch's current stream, asynchronously.
+
+Two layout seams are hidden here.  The tensor core reads block scales in a
+128-row x 4-group atom order and reads the LoRA activations as 16-bit values,
+while the API tensors are the reference's canonical `[K/16, rows]` scales and an
+fp32 `lora_act`.  The quantizer therefore also writes both twins and attaches
+them to the tensors it returns; `gemm_w4a4` picks them up when the tensors
+arrive unmodified, and otherwise (tensors from elsewhere, e.g. weight scales)
+derives them once with two small kernels of the same library and caches them
+on the tensor object.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_DT = {torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_F32}
+_TWIN = "_svdq_twin"   # attribute name: (tensor, version of the owner when it was made)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _attach(owner: torch.Tensor, twin: torch.Tensor) -> None:
+    setattr(owner, _TWIN, (twin, owner._version, owner.data_ptr()))
+
+
+def _attached(owner: torch.Tensor) -> Optional[torch.Tensor]:
+    rec = getattr(owner, _TWIN, None)
+    if rec is None:
+        return None
+    twin, version, ptr = rec
+    if owner._version != version or owner.data_ptr() != ptr:
+        return None
+    return twin
+
+
+def quantize_w4a4_act_fuse_lora(
+    input: torch.Tensor,
+    lora_down: torch.Tensor,
+    smooth: Optional[torch.Tensor],
+    *,
+    fp4: bool = True,
+    pad_size: int = 256,
+    block_m: int = 64,          # accepted for call-site compatibility; the kernel picks its own tiling
+    block_n: int = 64,
+    k_splits: Optional[int] = None,
+    _force: int = _lib.QUANT_AUTO,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    assert input.dim() == 2 and lora_down.dim() == 2
+    assert input.is_cuda and lora_down.is_cuda
+    assert input.dtype == lora_down.dtype
+    assert input.dtype in (torch.float16, torch.bfloat16)
+    M, K = input.shape
+    K2, R = lora_down.shape
+    assert K == K2, f"K mismatch: input K={K}, lora_down K={K2}"
+    assert K % 16 == 0, "NVFP4 group size is 16; K must be divisible by 16"
+    if smooth is not None:
+        assert smooth.is_cuda and smooth.dtype == input.dtype
+        assert smooth.shape == (K,)
+    if not fp4:
+        raise NotImplementedError("INT4 branch pending; for now only fp4=True.")
+    assert pad_size >= 1
+
+    lib = _lib.load()
+    dev = input.device
+    M_pad = ((M + pad_size - 1) // pad_size) * pad_size
+    x = input.contiguous()
+    ld = lora_down.contiguous()
+    sm = None if smooth is None else smooth.contiguous()
+    act = torch.empty((M_pad, K // 2), dtype=torch.uint8, device=dev)
+    ascales = torch.empty((K // 16, M_pad), dtype=torch.float8_e4m3fn, device=dev)
+    lora_act = torch.empty((M_pad, R), dtype=torch.float32, device=dev)
+    want_swz = M_pad % 128 == 0 and K % 64 == 0 and M_pad > 0
+    swz = torch.empty(M_pad * (K // 16), dtype=torch.uint8, device=dev) if want_swz else None
+    la16 = torch.empty((M_pad, R), dtype=input.dtype, device=dev) if R > 0 else None
+    with torch.cuda.device(dev):
+        rc = lib.svdq_quantize_w4a4_act_fuse_lora(
+            _ptr(x), _ptr(ld), _ptr(sm), _ptr(act), _ptr(ascales), _ptr(lora_act), _ptr(swz), _ptr(la16),
+            M, K, R, M_pad, _DT[input.dtype], _force, _stream(dev))
+    _lib.check(rc, "quantize_w4a4_act_fuse_lora")
+    if swz is not None:
+        _attach(ascales, swz)
+    if la16 is not None:
+        _attach(lora_act, la16)
+    return act, ascales, lora_act
+
+
+def quantize_nvfp4_rows(x: torch.Tensor, *, pad_size: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
+    """GPU row packer: `[rows, K]` f16/bf16/f32 -> (`[rows_pad, K/2]` u8, `[K/16, rows_pad]` e4m3)."""
+    assert x.dim() == 2 and x.is_cuda
+    assert x.dtype in _DT
+    rows, K = x.shape
+    assert K % 16 == 0, "NVFP4 group size is 16"
+    lib = _lib.load()
+    dev = x.device
+    rows_pad = ((rows + pad_size - 1) // pad_size) * pad_size
+    xc = x.contiguous()
+    packed = torch.empty((rows_pad, K // 2), dtype=torch.uint8, device=dev)
+    scales = torch.empty((K // 16, rows_pad), dtype=torch.float8_e4m3fn, device=dev)
+    want_swz = rows_pad % 128 == 0 and K % 64 == 0 and rows_pad > 0
+    swz = torch.empty(rows_pad * (K // 16), dtype=torch.uint8, device=dev) if want_swz else None
+    with torch.cuda.device(dev):
+        rc = lib.svdq_quantize_nvfp4_rows(_ptr(xc), _ptr(packed), _ptr(scales), _ptr(swz), rows, rows_pad, K,
+                                          _DT[x.dtype], _stream(dev))
+    _lib.check(rc, "quantize_nvfp4_rows")
+    if swz is not None:
+        _attach(scales, swz)
+    return packed, scales
+
+
+def swizzle_scales(scales: torch.Tensor) -> torch.Tensor:
+    """Canonical `[K/16, rows]` e4m3 scales -> flat uint8 in tensor-core atom order (cached on the tensor)."""
+    twin = _attached(scales)
+    if twin is not None:
+        return twin
+    G, rows = scales.shape
+    assert rows % 128 == 0, f"CUTLASS SF atom: M ({rows}) must be a multiple of 128"
+    assert G % 4 == 0, f"CUTLASS SF atom: K/16 ({G}) must be a multiple of 4"
+    lib = _lib.load()
+    src = scales.contiguous()
+    out = torch.empty(G * rows, dtype=torch.uint8, device=scales.device)
+    with torch.cuda.device(scales.device):
+        rc = lib.svdq_swizzle_scales(_ptr(src), _ptr(out), G, rows, _stream(scales.device))
+    _lib.check(rc, "swizzle_scales")
+    _attach(scales, out)
+    return out
+
+
+def _lora_act_16(lora_act_in: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    if lora_act_in.dtype == out_dtype:
+        return lora_act_in.contiguous()
+    twin = _attached(lora_act_in)
+    if twin is not None and twin.dtype == out_dtype:
+        return twin
+    assert lora_act_in.dtype == torch.float32, "lora_act_in must be fp32 or already out_dtype"
+    lib = _lib.load()
+    src = lora_act_in.contiguous()
+    out = torch.empty(src.shape, dtype=out_dtype, device=src.device)
+    with torch.cuda.device(src.device):
+        rc = lib.svdq_cast_lora_act(_ptr(src), _ptr(out), src.numel(), _DT[out_dtype], _stream(src.device))
+    _lib.check(rc, "cast_lora_act")
+    return out
+
+
+def gemm_w4a4(
+    act: torch.Tensor,
+    wgt: torch.Tensor,
+    ascales: torch.Tensor,
+    wscales: torch.Tensor,
+    lora_act_in: Optional[torch.Tensor] = None,
+    lora_up: Optional[torch.Tensor] = None,
+    wcscales: Optional[torch.Tensor] = None,
+    bias: Optional[torch.Tensor] = None,
+    out_dtype: Optional[torch.dtype] = None,
+    *,
+    use_2cta: bool = False,                 # accepted for call-site compatibility
+    tiler_mn: Optional[Tuple[int, int]] = None,
+    lora_schedule: str = "interleave",
+) -> torch.Tensor:
+    if out_dtype is None:
+        out_dtype = lora_up.dtype if lora_up is not None else torch.float16
+    assert act.is_cuda and wgt.is_cuda and ascales.is_cuda and wscales.is_cuda, "all inputs must live on CUDA"
+    assert act.dtype == torch.uint8 and wgt.dtype == torch.uint8, \
+        f"act/wgt must be uint8 NVFP4-packed; got {act.dtype}/{wgt.dtype}"
+    assert ascales.dtype == torch.float8_e4m3fn and wscales.dtype == torch.float8_e4m3fn, \
+        f"scales must be fp8_e4m3fn; got {ascales.dtype}/{wscales.dtype}"
+    assert out_dtype in (torch.float16, torch.bfloat16), f"out_dtype must be fp16 or bf16; got {out_dtype}"
+    M, K_half = act.shape
+    N, K_half_w = wgt.shape
+    assert K_half == K_half_w, f"act/wgt K disagree: {K_half} vs {K_half_w}"
+    K = K_half * 2
+    assert K % 16 == 0, f"K ({K}) must be a multiple of 16"
+    G = K // 16
+    assert ascales.shape == (G, M), f"ascales shape {tuple(ascales.shape)} != ({G}, {M})"
+    assert wscales.shape == (G, N), f"wscales shape {tuple(wscales.shape)} != ({G}, {N})"
+    assert (lora_act_in is None) == (lora_up is None), "lora_act_in and lora_up must both be provided or both None"
+    R = 0
+    if lora_act_in is not None:
+        assert lora_act_in.is_cuda and lora_up.is_cuda, "LoRA inputs must live on CUDA"
+        assert lora_act_in.shape[0] == M, f"lora_act_in shape {tuple(lora_act_in.shape)} row != M ({M})"
+        assert lora_up.shape[0] == N, f"lora_up shape {tuple(lora_up.shape)} row != N ({N})"
+        R = lora_act_in.shape[1]
+        assert lora_up.shape[1] == R, f"lora_act_in/lora_up R disagree: {lora_act_in.shape[1]} vs {lora_up.shape[1]}"
+        assert R % 16 == 0, f"R ({R}) must be a multiple of LoRA atom K (16)"
+        assert lora_up.dtype == out_dtype, f"lora_up dtype {lora_up.dtype} must match out_dtype {out_dtype}"
+    if wcscales is not None:
+        assert wcscales.shape == (N,), f"wcscales must be [N]; got {tuple(wcscales.shape)}"
+    if bias is not None:
+        assert bias.shape == (N,), f"bias must be [N]; got {tuple(bias.shape)}"
+    assert M % 128 == 0, f"M ({M}) must be a multiple of 128"
+    assert N % 128 == 0, f"N ({N}) must be a multiple of 128"
+    assert K % 64 == 0, f"K ({K}) must be a multiple of 64 for NVFP4 scale atoms"
+    variant = 0
+    if tiler_mn is not None:
+        assert tiler_mn[1] in (128, 256) and N % tiler_mn[1] == 0
+        variant = tiler_mn[1]
+
+    lib = _lib.load()
+    dev = act.device
+    a = act.contiguous()
+    w = wgt.contiguous()
+    sa = swizzle_scales(ascales)
+    sw = swizzle_scales(wscales)
+    la = lu = None
+    if R > 0:
+        la = _lora_act_16(lora_act_in, out_dtype)
+        lu = lora_up.contiguous()
+    wc = None if wcscales is None else wcscales.to(out_dtype).contiguous()
+    b = None if bias is None else bias.to(out_dtype).contiguous()
+    y = torch.empty((M, N), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.svdq_gemm_w4a4(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(wc), _ptr(b), _ptr(y),
+                                M, N, K, R, _DT[out_dtype], variant, _stream(dev))
+    _lib.check(rc, "gemm_w4a4")
+    return y
+
+
+launch_v2 = gemm_w4a4   # the reference's name for the same entry point
+
+
+class LinearPlan:
+    """Host-buffer form of the whole linear (x on the host in, y on the host out).
+
+    Weights are uploaded once; `forward_host` copies x to the device, runs the
+    quantizer and the GEMM, copies y back and waits.  Thin wrapper over
+    svdq_linear_plan_* of the C ABI.
+    """
+
+    def __init__(self, max_M: int, K: int, N: int, R: int, dtype: torch.dtype, *, wgt, wscales, lora_down=None,
+                 lora_up=None, smooth=None, wcscales=None, bias=None, device: Optional[int] = None):
+        import ctypes
+        self._lib = _lib.load()
+        self._handle = ctypes.c_void_p()
+        self.max_M, self.K, self.N, self.R, self.dtype = max_M, K, N, R, dtype
+        self.device = torch.cuda.current_device() if device is None else device
+
+        def host(t):
+            return None if t is None else t.detach().cpu().contiguous()
+
+        keep = [host(t) for t in (wgt, wscales, lora_down, lora_up, smooth, wcscales, bias)]
+        with torch.cuda.device(self.device):
+            rc = self._lib.svdq_linear_plan_create(ctypes.byref(self._handle), max_M, K, N, R, _DT[dtype],
+                                                   *[_ptr(t) for t in keep])
+        _lib.check(rc, "linear_plan_create")
+
+    def forward_host(self, x_host: torch.Tensor, y_host: torch.Tensor) -> torch.Tensor:
+        assert not x_host.is_cuda and not y_host.is_cuda
+        assert x_host.is_contiguous() and y_host.is_contiguous()
+        M = x_host.shape[0]
+        assert x_host.shape == (M, self.K) and y_host.shape == (M, self.N)
+        assert x_host.dtype == self.dtype and y_host.dtype == self.dtype
+        with torch.cuda.device(self.device):
+            rc = self._lib.svdq_linear_plan_forward_host(self._handle, _ptr(x_host), _ptr(y_host), M)
+        _lib.check(rc, "linear_plan_forward_host")
+        return y_host
+
+    def close(self) -> None:
+        if self._handle:
+            self._lib.svdq_linear_plan_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass

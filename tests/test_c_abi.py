@@ -1,0 +1,73 @@
+"""The C ABI without a GPU: the library loads, exports exactly what the header
+declares, and rejects bad arguments before touching CUDA."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "svdq_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(svdq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_table_agree():
+    from svdquant_kernels_b200 import _lib
+    assert _declared_functions() == sorted(_lib.SIGNATURES)
+
+
+def test_library_exports_every_declared_symbol(lib_path):
+    lib = ctypes.CDLL(lib_path)
+    for name in _declared_functions():
+        assert hasattr(lib, name), f"{name} is declared in include/svdq_b200.h but not exported"
+
+
+def test_status_strings(lib_path):
+    from svdquant_kernels_b200 import _lib
+    assert _lib.status_string(0) == "ok"
+    assert "contract" in _lib.status_string(2)
+    assert _lib.load().svdq_version() >= 100
+
+
+def test_argument_validation_needs_no_device(lib_path):
+    from svdquant_kernels_b200 import _lib
+    lib = _lib.load()
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf)
+    p = (p + 15) & ~15
+    # K not a multiple of 16
+    assert lib.svdq_quantize_w4a4_act_fuse_lora(p, p, None, p, p, p, None, None, 4, 24, 0, 4, 0, 0, None) == 2
+    # unsupported dtype
+    assert lib.svdq_quantize_w4a4_act_fuse_lora(p, p, None, p, p, p, None, None, 4, 32, 0, 4, 2, 0, None) == 3
+    # missing output
+    assert lib.svdq_quantize_w4a4_act_fuse_lora(p, p, None, None, p, p, None, None, 4, 32, 0, 4, 0, 0, None) == 1
+    # misaligned input
+    assert lib.svdq_quantize_w4a4_act_fuse_lora(p + 2, p, None, p, p, p, None, None, 4, 32, 0, 4, 0, 0, None) == 4
+    # empty problem is a no-op
+    assert lib.svdq_quantize_w4a4_act_fuse_lora(None, None, None, None, None, None, None, None, 0, 32, 0, 0, 0, 0, None) == 0
+    # GEMM contract
+    assert lib.svdq_gemm_w4a4_supported(256, 128, 128, 16) == 1
+    assert lib.svdq_gemm_w4a4_supported(4352, 15360, 3840, 128) == 1
+    assert lib.svdq_gemm_w4a4_supported(100, 128, 128, 16) == 0
+    assert lib.svdq_gemm_w4a4_supported(256, 128, 96, 16) == 0
+    assert lib.svdq_gemm_w4a4_supported(256, 128, 128, 8) == 0
+    assert lib.svdq_gemm_w4a4(p, p, p, p, None, None, None, None, p, 100, 128, 128, 0, 0, 0, None) == 2
+    assert lib.svdq_gemm_w4a4(p, p, p, p, p, None, None, None, p, 128, 128, 128, 16, 0, 0, None) == 1
+    assert lib.svdq_gemm_w4a4(p, p, p, p, None, None, None, None, p, 128, 128, 128, 0, 5, 0, None) == 3
+    assert lib.svdq_swizzle_scales(p, p, 6, 128, None) == 2
+
+
+def test_operator_asserts_mirror_the_reference(lib_path):
+    """Contract violations raise AssertionError / NotImplementedError like the reference's host code."""
+    import torch
+    from svdquant_kernels_b200 import ops
+    x = torch.zeros(4, 32, dtype=torch.float16)
+    with pytest.raises(AssertionError):
+        ops.quantize_w4a4_act_fuse_lora(x, torch.zeros(32, 16, dtype=torch.float16), None)   # not on CUDA
+    with pytest.raises(AssertionError):
+        ops.gemm_w4a4(torch.zeros(128, 64, dtype=torch.uint8), torch.zeros(128, 64, dtype=torch.uint8),
+                      torch.zeros(8, 128), torch.zeros(8, 128))

@@ -1,0 +1,104 @@
+"""The oracle against fixtures produced by the reference itself (CPU only)."""
+import numpy as np
+import pytest
+
+from conftest import golden_names, load_golden
+from oracle import nvfp4_oracle as O
+
+
+def test_e4m3_table_known_values():
+    dec = O.e4m3_decode(np.arange(256, dtype=np.uint8))
+    assert dec[0] == 0.0 and dec[1] == 2.0 ** -9 and dec[0x08] == 2.0 ** -6
+    assert dec[0x38] == 1.0 and dec[0x7E] == 448.0 and np.isnan(dec[0x7F])
+    assert dec[0x80 + 0x38] == -1.0
+
+
+def test_e4m3_encode_roundtrip_and_ties():
+    codes = np.arange(127, dtype=np.uint8)
+    vals = O.e4m3_decode(codes)
+    assert (O.e4m3_encode(vals) == codes).all()
+    # the clamp floor rounds to zero; midpoints go to the even code; 448 stays
+    assert O.e4m3_encode(np.float32([1e-12]))[0] == 0
+    assert O.e4m3_encode(np.float32([2.0 ** -10]))[0] == 0            # tie between 0 and 2^-9 -> even (0)
+    assert O.e4m3_encode(np.float32([1.0001 * 2.0 ** -10]))[0] == 1
+    assert O.e4m3_encode(np.float32([0.06640625]))[0] == O.e4m3_encode(np.float32([0.0625]))[0]
+    assert O.e4m3_encode(np.float32([448.0]))[0] == 0x7E
+    mids = O._E4M3_MID.astype(np.float32)
+    got = O.e4m3_encode(mids)
+    assert (got % 2 == 0).all()
+
+
+def test_e2m1_rounds_ties_away_and_saturates():
+    v = np.float32([0.0, 0.2499, 0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, 7.0, 1e9, np.inf, np.nan, -0.0, -0.1, -0.25, -np.inf])
+    want = [0, 0, 1, 2, 3, 4, 5, 6, 7, 7, 7, 7, 7, 0, 0, 8, 9, 15]
+    assert O.e2m1_codes(v).tolist() == want
+
+
+def test_pack_is_low_nibble_even_k():
+    codes = np.arange(16, dtype=np.uint8)[None, :]
+    packed = O.pack_nibbles(codes)
+    assert packed[0, 0] == 0x10 and packed[0, 7] == 0xFE
+    assert (O.unpack_nibbles(packed) == codes).all()
+
+
+def test_zero_and_tiny_groups():
+    x = np.zeros((2, 32), dtype=np.float32)
+    x[1, :16] = 1e-4
+    x[1, 3] = -1e-4
+    x[1, 5] = 0.0
+    packed, scales = O.quantize_nvfp4_rows(x, 4)
+    assert packed.shape == (4, 16) and scales.shape == (2, 4)
+    assert (packed[0] == 0).all() and (packed[2:] == 0).all() and (scales == 0).all()
+    codes = O.unpack_nibbles(packed)[1, :16]
+    assert codes[0] == 7 and codes[3] == 15 and codes[5] == 0
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_quantizer_matches_reference_fixture(name):
+    g = load_golden(name)
+    act, ascales, lora = O.quantize_w4a4_act_fuse_lora(g["x"], g["lora_down"], g.get("smooth"), g["dtype"])
+    assert act.shape == g["act"].shape and ascales.shape == g["ascales"].shape
+    assert (act == g["act"]).all(), "codes must be bit-exact"
+    assert (ascales == g["ascales"]).all(), "scales must be bit-exact"
+    assert O.rel_l2(lora, g["lora_act"]) <= 1e-6
+    M = g["M"]
+    assert (lora[M:] == 0).all() and (act[M:] == 0).all() and (ascales[:, M:] == 0).all()
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_weight_packer_and_dequant_match_reference_fixture(name):
+    g = load_golden(name)
+    wgt, wscales = O.quantize_nvfp4_rows(g["w"], 1)
+    assert (wgt == g["wgt"]).all() and (wscales == g["wscales"]).all()
+    if "act_dequant" in g:
+        assert (O.dequantize_nvfp4_rows(g["act"], g["ascales"]) == g["act_dequant"]).all()
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_gemm_matches_reference_fixture(name):
+    g = load_golden(name)
+    dt = g["dtype"]
+    y, _, _, _ = O.gemm_w4a4(g["act"], g["wgt"], g["ascales"], g["wscales"], g["lora_act"], g["lora_up"],
+                             g["wcscales"], g["bias"], dt)
+    # both sides round an fp32 matmul to 16 bit; only the summation order of the fp32 BLAS differs
+    tol = 2e-5 if dt == "fp16" else 1e-4
+    assert O.rel_l2(O.bits_to_f32(y, dt), O.bits_to_f32(g["y"], dt)) <= tol
+    assert (y == g["y"]).mean() > 0.99
+    y2, _, _, _ = O.gemm_w4a4(g["act"], g["wgt"], g["ascales"], g["wscales"], g["lora_act"], g["lora_up"], None, None, dt)
+    assert O.rel_l2(O.bits_to_f32(y2, dt), O.bits_to_f32(g["y_plain"], dt)) <= tol
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_scale_atom_order_matches_reference_fixture(name):
+    g = load_golden(name)
+    if "ascales_atom" not in g:
+        pytest.skip("shape has no whole atoms")
+    assert (O.swizzle_scales(g["ascales"]) == g["ascales_atom"]).all()
+
+
+def test_bf16_rounding_is_nearest_even():
+    x = np.float32([1.0, 1.00390625, 1.01171875, -1.00390625, 3.4028235e38])
+    bits = O.f32_to_bits(x, "bf16")
+    back = O.bits_to_f32(bits, "bf16")
+    assert back[0] == 1.0 and back[1] == 1.0 and back[2] == np.float32(1.015625) and back[3] == -1.0
+    assert np.isinf(back[4])
