@@ -1,0 +1,377 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A4 linear hot path (quantizer + GEMM) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config c1] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  A step = one pass of the hot path over one
+batch: quantize_w4a4_act_fuse_lora followed by gemm_w4a4 on a 4352-row slab.
+With N > 1 (torchrun, one rank per GPU) every rank owns its own slab of rows
+and a replica of the weights; there is no data-path collective, so the job is
+weak-scaled and `value` is the sum over ranks divided by the slowest rank's
+time.
+
+`value`  : TFLOP/s of 2*M*N*K (LoRA FLOPs excluded, the reference's convention)
+           with inputs resident in HBM.
+`e2e`    : the same metric through the host-buffer C-ABI call: pinned host x in,
+           pinned host y out, both copies inside the timed region.
+`roofline`: the GEMM kernel alone (CUDA events around its launches inside the
+           timed loop); `roofline_quantizer`: the quantizer alone, HBM-bound.
+`--impl reference` times the CPU oracle (the reference's PyTorch path restated
+in numpy; the reference itself is Python and is not shipped to the GPU box).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+NSETS = 6  # rotating input/output sets: 6 x ~70 MB is > 3 x the 126 MB L2
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs.
+
+    NVML is initialised in the constructor (before the timed region); one sample is taken at
+    start() and one at stop() so that even a millisecond-long region has samples inside it."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.samples, self.reasons, self.max_mhz, self.h, self.nv = [], set(), None, None, None
+        self._stop_evt = threading.Event()
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            # NVML enumerates physical devices; honour CUDA_VISIBLE_DEVICES when it is a plain index list
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if vis and all(v.strip().isdigit() for v in vis.split(",")):
+                index = int(vis.split(",")[index])
+            self.h = nv.nvmlDeviceGetHandleByIndex(index)
+            self.nv = nv
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
+            self.names = {
+                nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+            }
+        except Exception as e:  # NVML missing: report it instead of clocks
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def sample(self):
+        if self.nv is None:
+            return
+        try:
+            self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.h, self.nv.NVML_CLOCK_SM))
+            r = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            for bit, name in self.names.items():
+                if r & bit:
+                    self.reasons.add(name)
+        except Exception as e:
+            self.reasons.add(f"nvml_error:{type(e).__name__}")
+
+    def run(self):
+        while not self._stop_evt.is_set():
+            self.sample()
+            time.sleep(0.002)
+
+    def stop(self):
+        self.sample()
+        self._stop_evt.set()
+        self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def _np_bits(t):
+    import numpy as np
+    import torch
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+def run_reference(args):
+    """CPU arm: the oracle (numpy restatement of the reference's PyTorch path) on a bounded row sample."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    import torch
+    from oracle import nvfp4_oracle as O
+    from svdquant_kernels_b200.workloads import CONFIGS, make_inputs
+    shape = CONFIGS[args.config]
+    rows = min(shape.M, args.cpu_rows)
+    inp = make_inputs(shape, m_rows=rows)
+    name = "fp16" if shape.dtype == torch.float16 else "bf16"
+    wgt, wsc = O.quantize_nvfp4_rows(inp.w.numpy(), 1)
+    xb, ldb, smb = _np_bits(inp.x), _np_bits(inp.lora_down), _np_bits(inp.smooth)
+    lub, wcb, bb = _np_bits(inp.lora_up), _np_bits(inp.wcscales), _np_bits(inp.bias)
+
+    def step():
+        act, asc, la = O.quantize_w4a4_act_fuse_lora(xb, ldb, smb, name)
+        return O.gemm_w4a4(act, wgt, asc, wsc, la, lub, wcb, bb, name)[0]
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    m_pad = -(-rows // 256) * 256
+    tflops = 2.0 * m_pad * shape.N * shape.K / dt / 1e12
+    try:
+        from threadpoolctl import threadpool_info
+        cores = max([p.get("num_threads", 1) for p in threadpool_info()] + [1])
+    except Exception:
+        cores = os.cpu_count()
+    line = {
+        "impl": "reference", "metric": "w4a4_linear_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"{shape.name}: W4A4 linear M={shape.M} K={shape.K} N={shape.N} R={shape.R} {name}",
+                   "rows_per_step": rows},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": f"first {rows} of {shape.M} rows per step (quantizer + GEMM oracle, numpy/BLAS)"},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from svdquant_kernels_b200 import _lib, ops
+    from svdquant_kernels_b200.workloads import CONFIGS, gemm_flops, make_inputs, quantizer_bytes
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path for the product kernels")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    shape = CONFIGS[args.config]
+    name = "fp16" if shape.dtype == torch.float16 else "bf16"
+    # every rank: its own rows, the same weights
+    inp = make_inputs(shape, row_offset=rank)
+    M, K, N, R = shape.M, shape.K, shape.N, shape.R
+    M_pad = -(-M // 256) * 256
+    wgt, wsc = ops.quantize_nvfp4_rows(inp.w.to(dev), pad_size=1)
+    ops.swizzle_scales(wsc)
+    ld, lu = inp.lora_down.to(dev), inp.lora_up.to(dev)
+    sm, wc, bias = inp.smooth.to(dev), inp.wcscales.to(dev), inp.bias.to(dev)
+    xs = [inp.x.to(dev)]
+    for i in range(1, NSETS):
+        xs.append(xs[0].roll(i, dims=0).contiguous())
+
+    def quant(i):
+        return ops.quantize_w4a4_act_fuse_lora(xs[i % NSETS], ld, sm)
+
+    def gemm(q):
+        act, asc, la = q
+        return ops.gemm_w4a4(act, wgt, asc, wsc, la, lu, wc, bias, shape.dtype)
+
+    def step(i):
+        return gemm(quant(i))
+
+    ys = [None] * NSETS
+    for i in range(max(args.warmup, 3)):
+        ys[i % NSETS] = step(i)
+    torch.cuda.synchronize()
+    rc, words = _lib.device_status()
+    if rc != 0:
+        raise SystemExit(f"device status after warm-up: {words}")
+
+    # Each step is two kernels of ~10-100 us, so the launches are captured once per
+    # buffer set in CUDA graphs (one for the quantizer, one for the GEMM) and the timed
+    # loop only replays them; events between the replays give the per-kernel durations.
+    use_graphs = not args.no_graphs
+    launch_q = launch_g = None
+    if use_graphs:
+        try:
+            gq, gg, qs = [], [], []
+            for s_ in range(NSETS):
+                g1 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g1):
+                    q = quant(s_)
+                g2 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g2):
+                    ys[s_] = gemm(q)
+                gq.append(g1); gg.append(g2); qs.append(q)
+            launch_q = lambda i: gq[i % NSETS].replay()
+            launch_g = lambda i: gg[i % NSETS].replay()
+            for i in range(NSETS):
+                launch_q(i); launch_g(i)
+            torch.cuda.synchronize()
+        except Exception as e:  # capture refused: fall back to eager launches and say so
+            use_graphs = False
+            graph_note = f"graph capture failed ({type(e).__name__}: {e}); eager launches"
+    if not use_graphs:
+        cur = {}
+        def launch_q(i):
+            cur["q"] = quant(i)
+        def launch_g(i):
+            ys[i % NSETS] = gemm(cur["q"])
+    graph_note = "CUDA-graph replays" if use_graphs else locals().get("graph_note", "eager launches")
+
+    # ---- timed region: K steps, inputs resident in HBM ----
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    sampler = ClockSampler(local)
+    sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        if i == args.steps // 2:
+            sampler.sample()     # at least one sample while the queue is full
+        ev[i][0].record()
+        launch_q(i)
+        ev[i][1].record()
+        launch_g(i)
+        ev[i][2].record()
+    end.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop()
+    total_ms = start.elapsed_time(end)
+    q_us = sum(e[0].elapsed_time(e[1]) for e in ev) / args.steps * 1e3
+    g_us = sum(e[1].elapsed_time(e[2]) for e in ev) / args.steps * 1e3
+    rc, words = _lib.device_status()
+    if rc != 0:
+        raise SystemExit(f"device status after the timed region: {words}")
+
+    # ---- end to end: host buffers through the C-ABI plan ----
+    wgt_h, wsc_h = wgt.cpu(), wsc.view(torch.uint8).cpu()
+    plan = ops.LinearPlan(M, K, N, R, shape.dtype, wgt=wgt_h, wscales=wsc_h, lora_down=inp.lora_down,
+                          lora_up=inp.lora_up, smooth=inp.smooth, wcscales=inp.wcscales, bias=inp.bias, device=local)
+    xh = [inp.x.pin_memory(), inp.x.roll(1, dims=0).contiguous().pin_memory()]
+    yh = [torch.empty((M, N), dtype=shape.dtype).pin_memory() for _ in range(2)]
+    e2e_steps = max(3, min(args.steps, 50))
+    for i in range(2):
+        plan.forward_host(xh[i % 2], yh[i % 2])
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        plan.forward_host(xh[i % 2], yh[i % 2])      # returns after y is on the host
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    plan.close()
+    # sanity: both paths computed the same thing
+    y_dev = step(0)
+    torch.cuda.synchronize()
+    same = torch.equal(y_dev[:M].cpu(), yh[0])
+
+    t = torch.tensor([total_ms, q_us, g_us, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, q_us, g_us, e2e_ms = t.tolist()
+
+    peaks = _peaks()
+    flops = gemm_flops(M_pad, N, K)
+    qbytes = quantizer_bytes(M, K, R)
+    ms_per_step = total_ms / args.steps
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
+    g_tflops = flops / (g_us * 1e-6) / 1e12
+    q_gbs = qbytes / (q_us * 1e-6) / 1e9
+    nvfp4_peak = 4.0 * peaks["bf16_tflops"]
+    line = {
+        "metric": "w4a4_linear_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 accumulate)", "data": "synthetic",
+        "config": {
+            "workload": f"{shape.name}: W4A4 linear M={M} K={K} N={N} R={R} {name}, rows sharded over ranks, weights replicated",
+            "per_rank_rows": M, "launch": graph_note, "l2": f"rotating {NSETS} activation/output sets (> 3x L2) between steps",
+            "quantizer_us": q_us, "gemm_us": g_us, "pct_of_10pf_nominal": 100.0 * g_tflops / 10000.0,
+            "quantizer_pct_of_8tbs_nominal": 100.0 * q_gbs / 8000.0,
+        },
+        "roofline": {"bound": "tensor", "achieved": g_tflops, "peak": nvfp4_peak, "unit": "TFLOP/s",
+                     "frac": g_tflops / nvfp4_peak, "traffic": None,
+                     "kernel": "gemm_w4a4_kernel",
+                     "peak_note": f"4 x {peaks['source']} bf16 cuBLAS burst ({peaks['bf16_tflops']} TF/s): no NVFP4 figure is measured on this pool; "
+                                  "4 is the nominal nvfp4:bf16 rate ratio"},
+        "roofline_quantizer": {"bound": "hbm", "achieved": q_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                               "frac": q_gbs / peaks["hbm_gbs"], "traffic": None, "kernel": "quantize_fused_kernel",
+                               "peak_note": f"{peaks['source']} copy bandwidth"},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                "ms_per_step": e2e_ms, "steps": e2e_steps, "matches_device_path": bool(same)},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(shape, args)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(shape, args):
+    """The oracle on this box's host cores, on a bounded sample of the same workload."""
+    import torch
+    from oracle import nvfp4_oracle as O
+    from svdquant_kernels_b200.workloads import make_inputs
+    rows = min(shape.M, args.cpu_rows)
+    inp = make_inputs(shape, m_rows=rows)
+    name = "fp16" if shape.dtype == torch.float16 else "bf16"
+    wgt, wsc = O.quantize_nvfp4_rows(inp.w.numpy(), 1)
+    t0 = time.perf_counter()
+    reps = 0
+    while reps < 2 or (time.perf_counter() - t0 < 10.0 and reps < 50):
+        act, asc, la = O.quantize_w4a4_act_fuse_lora(_np_bits(inp.x), _np_bits(inp.lora_down), _np_bits(inp.smooth), name)
+        O.gemm_w4a4(act, wgt, asc, wsc, la, _np_bits(inp.lora_up), _np_bits(inp.wcscales), _np_bits(inp.bias), name)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    m_pad = -(-rows // 256) * 256
+    try:
+        from threadpoolctl import threadpool_info
+        cores = max([p.get("num_threads", 1) for p in threadpool_info()] + [1])
+    except Exception:
+        cores = os.cpu_count()
+    return {"value": 2.0 * m_pad * shape.N * shape.K / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"{reps} passes over the first {rows} of {shape.M} rows (quantizer + GEMM oracle, numpy/BLAS), {dt:.2f} s each"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--config", default="c1")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-rows", type=int, default=1024, help="rows per pass of the CPU oracle sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graphs", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

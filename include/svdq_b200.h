@@ -70,6 +70,14 @@ int svdq_quantize_w4a4_act_fuse_lora(const void* x, const void* lora_down, const
                                      int M, int K, int R, int M_pad, int dtype, int flags, void* stream);
 
 /*
+ * How many clusters of `k_split` CTAs (1, 2 or 4) of the fused quantizer the current device can
+ * keep resident at once for LoRA rank R; -1 on error.  Introspection for tuning; the reference
+ * has no counterpart (its Triton launch picks k_splits from a table,
+ * triton_kernels/quantize_w4a4_act_fuse_lora/kernel.py:344-378).
+ */
+int svdq_quantizer_max_active_clusters(int R, int k_split, int dtype);
+
+/*
  * NVFP4 row packer (weights: pad 1).
  * Stands in for quantize_nvfp4_rows(x, pad_size) (baseline/kernels/_nvfp4.py:60-95).
  *   x [rows, K] f16/bf16/f32 -> codes [rows_pad, K/2], scales [K/16, rows_pad],

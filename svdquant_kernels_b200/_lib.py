@@ -23,6 +23,7 @@ SIGNATURES = {
     "svdq_version": (c_int, []),
     "svdq_quantize_w4a4_act_fuse_lora": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "svdq_quantizer_max_active_clusters": (c_int, [c_int, c_int, c_int]),
     "svdq_quantize_nvfp4_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "svdq_swizzle_scales": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "svdq_cast_lora_act": (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_void_p]),

@@ -92,6 +92,11 @@ int svdq_cast_lora_act(const float* src, void* dst, long long count, int dtype, 
   return launch_cast_f32(src, dst, count, dtype, static_cast<cudaStream_t>(stream));
 }
 
+int svdq_quantizer_max_active_clusters(int R, int k_split, int dtype) {
+  if (k_split != 1 && k_split != 2 && k_split != 4) return -1;
+  return quantize_fused_max_clusters(R, k_split, dtype);
+}
+
 int svdq_gemm_w4a4_supported(int M, int N, int K, int R) { return gemm_supported(M, N, K, R) ? 1 : 0; }
 
 int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,

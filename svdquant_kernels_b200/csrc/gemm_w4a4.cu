@@ -25,6 +25,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <type_traits>
+#include <cstdlib>
 
 namespace svdq {
 
@@ -57,6 +58,7 @@ struct Params {
   void* y;              // [M, N]
   int M, N, K, R;
   int tiles_m, tiles_n;
+  int dbg;   // TEMP diagnostic switches
 };
 
 __device__ __forceinline__ uint32_t pack2(__half a, __half b) {
@@ -136,6 +138,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, it)) { ok = false; break; }
           uint8_t* st = smem + s * C::STAGE_BYTES;
+          if (p.dbg & 8) { mbar_arrive(&full[s]); continue; }
           if (kt < kt_main) {
             // codes past K are zero-filled by TMA (and still counted); scale atoms past K are not fetched
             const uint32_t nkb = min(4, k_groups4 - kt * 4);
@@ -180,10 +183,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (kt < kt_main) {
             const uint32_t sfa_addr = b_addr + C::B_BYTES;
             const uint32_t sfb_addr = sfa_addr + SFA_BYTES;
-            const int nkb = min(4, k_groups4 - kt * 4);
+            const int nkb = (p.dbg & 4) ? 0 : min(4, k_groups4 - kt * 4);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              if (j < nkb) {
+              if (j < nkb && !((p.dbg & 2) && kt > 0)) {
                 tmem_cp_scales<1>(tmem_sfa + j * 4, smem_desc(kDescSF, sfa_addr + j * 512));
 #pragma unroll
                 for (int h = 0; h < BN / 128; ++h)
@@ -196,7 +199,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                            kIdescMain, tmem_sfa + j * 4, tmem_sfb + j * (BN / 32), (kt | j) != 0 ? 1u : 0u);
           } else {
             const int r0 = (kt - kt_main) * 64;
-            const int nk = min(4, (p.R - r0) / 16);
+            const int nk = (p.dbg & 4) ? 0 : min(4, (p.R - r0) / 16);
             for (int j = 0; j < nk; ++j)
               mma_f16<1>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
                          kIdescLora, (kt | j) != 0 ? 1u : 0u);
@@ -243,8 +246,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           o[i] = pack2(from_f32<OutT>(a), from_f32<OutT>(b));
         }
         uint4* dst = reinterpret_cast<uint4*>(yrow + c0);
+        if (!(p.dbg & 1)) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -301,6 +306,7 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   p.wc = wc; p.bias = bias; p.y = y;
   p.M = M; p.N = N; p.K = K; p.R = R;
   p.tiles_m = M / gemm::BM; p.tiles_n = N / BN;
+  { const char* e = getenv("SVDQ_DEBUG"); p.dbg = e ? atoi(e) : 0; }
   auto kern = gemm::gemm_w4a4_kernel<BN, OutT>;
   static bool configured = false;
   if (!configured) {

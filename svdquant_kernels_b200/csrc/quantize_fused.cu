@@ -25,6 +25,7 @@
 #include "nvfp4_math.cuh"
 #include "sm100.cuh"
 #include "svdq_internal.h"
+#include <cstdlib>
 
 namespace svdq {
 namespace qf {
@@ -56,6 +57,7 @@ struct Params {
   float* lora;            // [M_pad, R]
   void* lora16;           // [M_pad, R] or null
   int M, K, R, M_pad;
+  int dbg;   // TEMP diagnostic switches
 };
 
 template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t v);
@@ -169,7 +171,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
         if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, i)) { ok = false; break; }
         tc_fence_after_sync();
-        if (p.R > 0) {
+        if (p.R > 0 && !(p.dbg & 64)) {
           const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
           const uint32_t b_addr = a_addr + X_BYTES;
 #pragma unroll
@@ -202,6 +204,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
 
+      if (p.dbg & 16) continue;
       const int kl = i * SLAB_K;              // column offset inside this CTA's range
       uint32_t codes[8];
       uint32_t sbytes = 0;
@@ -250,6 +253,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         codes[2 * g] = lo; codes[2 * g + 1] = hi;
       }
       const int k0 = k_begin + kl;
+      if ((p.dbg & 32) && codes[0] != 0x12345678u) continue;
       uint4* dst = reinterpret_cast<uint4*>(act_row + (k0 >> 1));
       dst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
       dst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
@@ -388,7 +392,8 @@ static int launch_qf(const void* x, const void* w, const qf::Params& p, cudaStre
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return SVDQ_ERR_LAUNCH;
     configured = true;
   }
-  const int ks = pick_k_split(p.M_pad, p.K);
+  int ks = pick_k_split(p.M_pad, p.K);
+  { const char* e = getenv("SVDQ_KS"); if (e) ks = atoi(e); }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.M_pad / qf::TILE_M, ks, 1);
   cfg.blockDim = dim3(qf::NUM_THREADS, 1, 1);
@@ -405,6 +410,30 @@ static int launch_qf(const void* x, const void* w, const qf::Params& p, cudaStre
   return SVDQ_OK;
 }
 
+template <typename T, int RP>
+static int max_clusters_t(int ks) {
+  using C = qf::Cfg<RP>;
+  auto kern = qf::quantize_fused_kernel<T, RP>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(64, ks, 1);
+  cfg.blockDim = dim3(qf::NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = ks; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return -1; }
+  return n;
+}
+
+int quantize_fused_max_clusters(int R, int ks, int dtype) {
+  const int rp = R <= 64 ? 64 : (R <= 128 ? 128 : 256);
+  if (dtype == SVDQ_DTYPE_F16) return rp == 64 ? max_clusters_t<__half, 64>(ks) : rp == 128 ? max_clusters_t<__half, 128>(ks) : max_clusters_t<__half, 256>(ks);
+  return rp == 64 ? max_clusters_t<__nv_bfloat16, 64>(ks) : rp == 128 ? max_clusters_t<__nv_bfloat16, 128>(ks) : max_clusters_t<__nv_bfloat16, 256>(ks);
+}
+
 int launch_quantize_fused(const void* x, const void* lora_down, const void* smooth, void* act, void* ascales,
                           float* lora_act, void* ascales_swz, void* lora_act16, int M, int K, int R, int M_pad,
                           int dtype, cudaStream_t stream) {
@@ -417,6 +446,7 @@ int launch_quantize_fused(const void* x, const void* lora_down, const void* smoo
   p.lora = lora_act;
   p.lora16 = lora_act16;
   p.M = M; p.K = K; p.R = R; p.M_pad = M_pad;
+  { const char* e = getenv("SVDQ_DEBUG"); p.dbg = e ? atoi(e) : 0; }
   const int rp = R <= 64 ? 64 : (R <= 128 ? 128 : 256);
   if (dtype == SVDQ_DTYPE_F16) {
     if (rp == 64) return launch_qf<__half, 64>(x, lora_down, p, stream);

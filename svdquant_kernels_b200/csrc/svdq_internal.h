@@ -23,6 +23,8 @@ int launch_quantize_fused(const void* x, const void* lora_down, const void* smoo
                           float* lora_act, void* ascales_swz, void* lora_act16, int M, int K, int R, int M_pad,
                           int dtype, cudaStream_t stream);
 
+int quantize_fused_max_clusters(int R, int ks, int dtype);
+
 // gemm_w4a4.cu
 bool gemm_supported(int M, int N, int K, int R);
 int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,

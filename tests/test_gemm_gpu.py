@@ -1,0 +1,133 @@
+"""GEMM parity on the GPU, through the C ABI, against the oracle's out-dtype
+result.  Tolerance: rel-L2 <= 1e-3 (the stated bound); the kernel differs from
+the oracle only by fp32 summation order and by feeding the LoRA product a
+16-bit lora_act (as the reference's own kernel does), observed ~1e-5 / ~2e-4."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_names, load_golden
+from helpers import NAME_DT, assert_device_clean, bits, from_bits, oracle_gemm, rel_l2_vs_bits, u8
+from oracle import nvfp4_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-3
+
+
+def _ops():
+    from svdquant_kernels_b200 import ops
+    return ops
+
+
+def _case(M, K, N, R, dtype, seed, wc=True, bias=True, tiler=None, act="gauss"):
+    ops = _ops()
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    if act == "gelu":
+        x = torch.nn.functional.gelu(x)
+    x[:, torch.randperm(K, generator=g)[:4]] *= 20
+    x = x.to(dtype)
+    sm = x.float().abs().amax(0).pow(0.5).clamp_min(1e-2).to(dtype)
+    w = torch.randn(N, K, generator=g) * 0.02 / sm.float()[None, :]
+    ld = (torch.randn(K, R, generator=g) / K ** 0.5).to(dtype)
+    lu = (torch.randn(N, R, generator=g) * 0.01).to(dtype)
+    b = (torch.randn(N, generator=g) * 0.01).to(dtype) if bias else None
+    c = (torch.rand(N, generator=g) + 0.5).to(dtype) if wc else None
+    dev = "cuda"
+    act_t, asc, la = ops.quantize_w4a4_act_fuse_lora(x.to(dev), ld.to(dev), sm.to(dev))
+    wgt, wsc = ops.quantize_nvfp4_rows(w.to(dev), pad_size=1)
+    has_lora = R > 0
+    y = ops.gemm_w4a4(act_t, wgt, asc, wsc, la if has_lora else None, lu.to(dev) if has_lora else None,
+                      None if c is None else c.to(dev), None if b is None else b.to(dev), dtype, tiler_mn=tiler)
+    torch.cuda.synchronize()
+    assert_device_clean()
+    y_bits, _ = oracle_gemm(u8(act_t), u8(wgt), u8(asc), u8(wsc), la.cpu().numpy() if has_lora else None,
+                            lu if has_lora else None, c, b, dtype)
+    assert tuple(y.shape) == y_bits.shape and y.dtype == dtype
+    return rel_l2_vs_bits(y, y_bits)
+
+
+@pytest.mark.parametrize("name", golden_names())
+def test_against_reference_fixtures(name):
+    g = load_golden(name)
+    if g["K"] % 64 != 0 or g["N"] % 128 != 0:
+        pytest.skip("outside the GEMM contract (K % 64, N % 128)")
+    ops = _ops()
+    dt = NAME_DT[g["dtype"]]
+    act = torch.from_numpy(g["act"]).cuda()
+    wgt = torch.from_numpy(g["wgt"]).cuda()
+    asc = torch.from_numpy(g["ascales"]).cuda().view(torch.float8_e4m3fn)
+    wsc = torch.from_numpy(g["wscales"]).cuda().view(torch.float8_e4m3fn)
+    la = torch.from_numpy(g["lora_act"]).cuda()
+    lu = from_bits(g["lora_up"], dt)
+    y = ops.gemm_w4a4(act, wgt, asc, wsc, la, lu, from_bits(g["wcscales"], dt), from_bits(g["bias"], dt), dt)
+    y2 = ops.gemm_w4a4(act, wgt, asc, wsc, la, lu, None, None, dt)
+    torch.cuda.synchronize()
+    assert_device_clean()
+    # The edge fixtures hold rows of huge activations whose LoRA term dominates y.  The LoRA product
+    # consumes lora_act rounded to 16 bit (as the reference's kernel does: kernel_v2_fa4.py:176-184),
+    # and bf16 keeps 8 bits, so there the bound is the reference's own recorded bf16 threshold
+    # (docs/gpu.md:135-137: bf16 rel <= 7e-3); everywhere else it is 1e-3.
+    tol = 7e-3 if (name.startswith("edge") and g["dtype"] == "bf16") else TOL
+    assert rel_l2_vs_bits(y, g["y"]) <= tol
+    assert rel_l2_vs_bits(y2, g["y_plain"]) <= tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N,R", [(64, 128, 128, 16), (128, 64, 128, 0), (256, 256, 256, 32), (300, 320, 384, 64),
+                                     (512, 1024, 512, 128), (1024, 3840, 768, 128), (256, 2560, 1280, 256)])
+def test_matches_oracle(M, K, N, R, dtype):
+    assert _case(M, K, N, R, dtype, seed=M + N) <= TOL
+
+
+@pytest.mark.parametrize("wc,bias", [(False, False), (True, False), (False, True)])
+def test_affine_switches(wc, bias):
+    assert _case(256, 512, 256, 32, torch.float16, seed=1, wc=wc, bias=bias) <= TOL
+
+
+@pytest.mark.parametrize("tiler", [(128, 128), (128, 256)])
+def test_both_n_tiles(tiler):
+    assert _case(384, 768, 512, 64, torch.bfloat16, seed=2, tiler=tiler) <= TOL
+
+
+def test_main_product_is_exact_without_lora():
+    """fp4 x fp4 products with e4m3 scales accumulate exactly in fp32 at this size, so the
+    kernel equals the oracle bit for bit (the reference recorded rel = 0 for its no-LoRA
+    kernel as well)."""
+    assert _case(256, 256, 256, 0, torch.float16, seed=4, wc=False, bias=False) <= 1e-6
+
+
+@pytest.mark.parametrize("cfg", ["c1", "c4"])
+def test_full_size_configs(cfg):
+    from svdquant_kernels_b200.workloads import CONFIGS
+    s = CONFIGS[cfg]
+    assert _case(s.M, s.K, s.N, s.R, s.dtype, seed=77) <= TOL
+
+
+def test_linearity_property_full_size():
+    """Size-independent check at the largest shape: doubling lora_up and bias-free output is additive,
+    y(lora) - y(no lora) equals the LoRA product alone, computed by torch in fp32."""
+    ops = _ops()
+    M, K, N, R = 4352, 3840, 15360, 128
+    g = torch.Generator().manual_seed(21)
+    dt = torch.bfloat16
+    x = torch.randn(M, K, generator=g).to(dt).cuda()
+    ld = (torch.randn(K, R, generator=g) / K ** 0.5).to(dt).cuda()
+    lu = (torch.randn(N, R, generator=g) * 0.01).to(dt).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.02).cuda()
+    act, asc, la = ops.quantize_w4a4_act_fuse_lora(x, ld, None)
+    wgt, wsc = ops.quantize_nvfp4_rows(w, pad_size=1)
+    y0 = ops.gemm_w4a4(act, wgt, asc, wsc, None, None, None, None, dt).float()
+    y1 = ops.gemm_w4a4(act, wgt, asc, wsc, la, lu, None, None, dt).float()
+    torch.cuda.synchronize()
+    assert_device_clean()
+    want = la.to(dt).float() @ lu.float().T
+    diff = (y1 - y0)
+    # both y are bf16-rounded, so compare against the size of y itself
+    err = (diff - want).norm() / y1.norm()
+    assert err.item() <= 6e-3
+    # and the main product alone against a dequantised fp32 matmul on a slab of rows
+    a = torch.from_numpy(O.dequantize_nvfp4_rows(u8(act[:256]), u8(asc[:, :256]))).cuda()
+    wd = torch.from_numpy(O.dequantize_nvfp4_rows(u8(wgt), u8(wsc))).cuda()
+    ref = (a @ wd.T).to(dt).float()
+    assert ((y0[:256] - ref).norm() / ref.norm()).item() <= TOL

@@ -1,0 +1,145 @@
+"""Quantizer parity on the GPU, through the C ABI: codes and scales bit-exact
+against the oracle and the reference-generated fixtures, lora_act within
+rel-L2 1e-3 (it is observed near 1e-7: fp32 accumulation of exact products)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_names, load_golden
+from helpers import NAME_DT, assert_device_clean, bits, from_bits, oracle_quantize, u8
+from oracle import nvfp4_oracle as O
+
+pytestmark = pytest.mark.gpu
+LORA_TOL = 1e-3
+GENERIC, FUSED = 1, 2
+
+
+def _ops():
+    from svdquant_kernels_b200 import ops
+    return ops
+
+
+def _check(x, ld, sm, force, pad=256):
+    ops = _ops()
+    act, ascales, lora = ops.quantize_w4a4_act_fuse_lora(x, ld, sm, fp4=True, pad_size=pad, _force=force)
+    torch.cuda.synchronize()
+    assert_device_clean()
+    o_act, o_sc, o_lora = oracle_quantize(x, ld, sm, pad)
+    assert act.dtype == torch.uint8 and ascales.dtype == torch.float8_e4m3fn and lora.dtype == torch.float32
+    assert tuple(act.shape) == o_act.shape and tuple(ascales.shape) == o_sc.shape and tuple(lora.shape) == o_lora.shape
+    assert int((u8(ascales) != o_sc).sum()) == 0, "scale bytes differ"
+    assert int((u8(act) != o_act).sum()) == 0, "code bytes differ"
+    if ld.shape[1] > 0:
+        assert O.rel_l2(lora.cpu().numpy(), o_lora) <= LORA_TOL
+    M = x.shape[0]
+    assert (lora[M:] == 0).all()
+    # the twins the GEMM consumes
+    twin = getattr(ascales, "_svdq_twin", None)
+    if twin is not None:
+        assert (twin[0].cpu().numpy() == O.swizzle_scales(o_sc)).all(), "swizzled scales differ"
+    twin16 = getattr(lora, "_svdq_twin", None)
+    if twin16 is not None and ld.shape[1] > 0:
+        want = O.f32_to_bits(lora.cpu().numpy(), "fp16" if x.dtype == torch.float16 else "bf16")
+        assert (bits(twin16[0]) == want).all(), "16-bit lora_act is not the rounded fp32 one"
+    return act, ascales, lora
+
+
+def _inputs(M, K, R, dtype, seed, smooth=True):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    x[:, torch.randperm(K, generator=g)[:4]] *= 20
+    x = x.to(dtype)
+    sm = x.float().abs().amax(0).pow(0.5).clamp_min(1e-2).to(dtype) if smooth else None
+    ld = (torch.randn(K, R, generator=g) / K ** 0.5).to(dtype)
+    return x.cuda(), ld.cuda(), None if sm is None else sm.cuda()
+
+
+@pytest.mark.parametrize("force", [GENERIC, FUSED])
+@pytest.mark.parametrize("name", golden_names())
+def test_against_reference_fixtures(name, force):
+    g = load_golden(name)
+    dt = NAME_DT[g["dtype"]]
+    if force == FUSED and g["K"] % 64 != 0:
+        pytest.skip("fused kernel takes K % 64 == 0")
+    x = from_bits(g["x"], dt)
+    ld = from_bits(g["lora_down"], dt)
+    sm = from_bits(g["smooth"], dt) if "smooth" in g else None
+    act, ascales, lora = _ops().quantize_w4a4_act_fuse_lora(x, ld, sm, _force=force)
+    torch.cuda.synchronize()
+    assert_device_clean()
+    assert (u8(act) == g["act"]).all() and (u8(ascales) == g["ascales"]).all()
+    assert O.rel_l2(lora.cpu().numpy(), g["lora_act"]) <= LORA_TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,R", [(64, 128, 16), (1, 64, 32), (300, 256, 32), (257, 1024, 128), (512, 3840, 128),
+                                   (700, 2560, 64), (130, 640, 256), (256, 192, 0)])
+def test_fused_matches_oracle(M, K, R, dtype):
+    x, ld, sm = _inputs(M, K, R, dtype, 100 + M + K)
+    _check(x, ld, sm, FUSED)
+    _check(x, ld, None, FUSED)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,R,pad", [(64, 128, 16, 256), (33, 48, 5, 1), (100, 80, 24, 16), (260, 528, 40, 256)])
+def test_generic_matches_oracle(M, K, R, pad, dtype):
+    x, ld, sm = _inputs(M, K, R, dtype, 7 + M)
+    _check(x, ld, sm, GENERIC, pad)
+
+
+@pytest.mark.parametrize("force", [GENERIC, FUSED])
+def test_edge_values(force):
+    """Exact ties, saturation, zero and sub-threshold groups, signed zeros, e4m3 subnormal and clamped scales."""
+    dtype = torch.float16
+    M, K, R = 128, 256, 16
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, K, generator=g)
+    x[0, :16] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0])
+    x[1, 16:32] = 0
+    x[2, 32:48] = 1e-4; x[2, 33] = -1e-4; x[2, 34] = 0
+    x[3, 48:64] = 0; x[3, 49] = -0.0
+    x[4, :16] = 3e-3
+    x[5, :16] = 2640.0
+    x[6, :16] = 6e4
+    x[7, :] = 0
+    for i in range(8, 40):           # a sweep of magnitudes so every e4m3 scale exponent shows up
+        x[i] *= 2.0 ** (i - 24)
+    x = x.to(dtype).cuda()
+    ld = (torch.randn(K, R, generator=g) / 16).to(dtype).cuda()
+    sm = torch.ones(K, dtype=dtype).cuda()
+    sm[64:] = (torch.rand(K - 64, generator=g) * 3 + 0.05).to(dtype).cuda()
+    _check(x, ld, sm, force)
+    _check(x, ld, None, force)
+
+
+def test_full_size_config_is_bit_exact():
+    """The benchmark shape (4352 x 3840, R = 128, fp16) against the oracle."""
+    from svdquant_kernels_b200.workloads import CONFIGS, make_inputs
+    inp = make_inputs(CONFIGS["c1"])
+    x, ld, sm = inp.x.cuda(), inp.lora_down.cuda(), inp.smooth.cuda()
+    _check(x, ld, sm, FUSED)
+
+
+def test_weight_packer_matches_oracle():
+    ops = _ops()
+    g = torch.Generator().manual_seed(3)
+    w = torch.randn(384, 640, generator=g) * 0.02
+    packed, scales = ops.quantize_nvfp4_rows(w.cuda(), pad_size=1)
+    o_p, o_s = O.quantize_nvfp4_rows(w.numpy(), 1)
+    assert (u8(packed) == o_p).all() and (u8(scales) == o_s).all()
+    for dt in (torch.float16, torch.bfloat16):
+        wd = w.to(dt)
+        packed, scales = ops.quantize_nvfp4_rows(wd.cuda(), pad_size=1)
+        o_p, o_s = O.quantize_nvfp4_rows(wd.float().numpy(), 1)
+        assert (u8(packed) == o_p).all() and (u8(scales) == o_s).all()
+
+
+def test_round_trip_property_full_size():
+    """Size-independent property: dequant(quant(x)) re-quantises to the same codes and scales."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(4352, 3840, generator=g)).to(torch.bfloat16).cuda()
+    p1, s1 = ops.quantize_nvfp4_rows(x, pad_size=256)
+    deq = torch.from_numpy(O.dequantize_nvfp4_rows(u8(p1), u8(s1))).cuda()
+    p2, s2 = ops.quantize_nvfp4_rows(deq, pad_size=256)
+    assert torch.equal(p1, p2) and torch.equal(s1.view(torch.uint8), s2.view(torch.uint8))
