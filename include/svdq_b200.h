@@ -47,6 +47,15 @@ const char* svdq_status_string(int status);
 int svdq_version(void);
 
 /*
+ * One-time preparation of a smoothing vector: writes {smooth[k], 1/smooth[k]} as K float pairs
+ * followed by one 8-byte flag word (so smooth_table holds 8*K + 8 bytes, 16-byte aligned).
+ * smooth is a per-layer constant, so callers build the table once and pass it with every
+ * quantizer call.  No counterpart in the reference, which divides inside its kernel
+ * (triton_kernels/quantize_w4a4_act_fuse_lora/kernel.py:153-158).
+ */
+int svdq_prepare_smooth(const void* smooth, void* smooth_table, int K, int dtype, void* stream);
+
+/*
  * Fused activation quantizer + LoRA-down.
  * Stands in for quantize_w4a4_act_fuse_lora(input, lora_down, smooth, fp4=True, pad_size)
  *   (triton_kernels/quantize_w4a4_act_fuse_lora/kernel.py:289-400; oracle
@@ -55,16 +64,22 @@ int svdq_version(void);
  *   x          [M, K]        f16/bf16, row-major, K % 16 == 0
  *   lora_down  [K, R]        same type (R may be 0, then lora_down may be NULL)
  *   smooth     [K] or NULL   same type
+ *   smooth_table  from svdq_prepare_smooth(smooth), or NULL; without it a smoothed call takes the
+ *                 generic (slower, CUDA-core) kernels
  *   act        [M_pad, K/2]  u8   two E2M1 codes per byte, even k in the low nibble
  *   ascales    [K/16, M_pad] u8   E4M3 bit patterns (the reference's transposed layout)
  *   lora_act   [M_pad, R]    f32  rows >= M are zero
  *   ascales_swz  optional, M_pad*K/16 bytes: the same scales in the 128-row x 4-group
  *                atom order the tensor core reads (needs M_pad % 128 == 0, K % 64 == 0)
- *   lora_act16   optional [M_pad, R] in x's type: lora_act rounded once to 16 bit
+ *   lora_act16   optional: lora_act in the 16-bit form svdq_gemm_w4a4 consumes (same format as
+ *                lora_up).  dtype f16: [M_pad, R] fp16, rounded once, magnitudes beyond 65504
+ *                clamped.  dtype bf16: [2, M_pad, R] bf16 = hi plane then lo plane with
+ *                hi = bf16(v), lo = bf16(v - hi)
  *   M_pad      rows of the outputs, >= M (the reference pads M up to a multiple of 256)
  * Rows M..M_pad-1 of act / ascales are written as zero bytes, as the oracle does.
  */
 int svdq_quantize_w4a4_act_fuse_lora(const void* x, const void* lora_down, const void* smooth,
+                                     const void* smooth_table,
                                      void* act, void* ascales, float* lora_act,
                                      void* ascales_swz, void* lora_act16,
                                      int M, int K, int R, int M_pad, int dtype, int flags, void* stream);
@@ -93,8 +108,9 @@ int svdq_quantize_nvfp4_rows(const void* x, void* codes, void* scales, void* sca
  */
 int svdq_swizzle_scales(const void* scales, void* scales_swz, int k_groups, int rows, void* stream);
 
-/* f32 -> f16/bf16 copy of lora_act (the cast launch_v2 does at
- * cute_kernels/gemm_w4a4/kernel_v2_fa4.py:176-184). */
+/* f32 lora_act (count = M * R values) -> its 16-bit form of type dtype, as described for lora_act16
+ * above; dst holds count values for f16, 2 * count for bf16 (stands in for the cast launch_v2 does
+ * at cute_kernels/gemm_w4a4/kernel_v2_fa4.py:176-184). */
 int svdq_cast_lora_act(const float* src, void* dst, long long count, int dtype, void* stream);
 
 /*
@@ -104,11 +120,13 @@ int svdq_cast_lora_act(const float* src, void* dst, long long count, int dtype, 
  *
  *   act         [M, K/2] u8        wgt        [N, K/2] u8
  *   ascales_swz  M*K/16 bytes      wscales_swz N*K/16 bytes   (atom order, see above)
- *   lora_act16  [M, R] f16/bf16 or NULL      lora_up [N, R] same type or NULL (both or neither)
+ *   lora_act16  16-bit form of lora_act for dtype (see above) or NULL
+ *   lora_up     [N, R] of type dtype or NULL (both or neither)
  *   wcscales    [N] or NULL        bias       [N] or NULL     (type = dtype)
  *   y           [M, N] dtype
  * Contract: M % 128 == 0, N % 128 == 0, K % 64 == 0, R % 16 == 0 (svdq_gemm_w4a4_supported).
- * variant: 0 = pick the N tile (256 when N % 256 == 0, else 128); 128 / 256 = force it.
+ * variant: 0 = let the library pick; 128 / 256 = one CTA per 128 x variant tile;
+ *          2128 / 2256 = CTA pairs on 256 x 128 / 256 x 256 tiles (needs M % 256 == 0).
  *   y = cast( (deq(act) deq(wgt)^T + lora_act16 lora_up^T) * wcscales + bias )
  */
 int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,

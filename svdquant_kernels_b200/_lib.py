@@ -21,8 +21,9 @@ OK = 0
 SIGNATURES = {
     "svdq_status_string": (c_char_p, [c_int]),
     "svdq_version": (c_int, []),
+    "svdq_prepare_smooth": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "svdq_quantize_w4a4_act_fuse_lora": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "svdq_quantizer_max_active_clusters": (c_int, [c_int, c_int, c_int]),
     "svdq_quantize_nvfp4_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "svdq_swizzle_scales": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),

@@ -44,7 +44,16 @@ const char* svdq_status_string(int status) {
 
 int svdq_version(void) { return 100; }
 
-int svdq_quantize_w4a4_act_fuse_lora(const void* x, const void* lora_down, const void* smooth, void* act,
+int svdq_prepare_smooth(const void* smooth, void* smooth_table, int K, int dtype, void* stream) {
+  if (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16) return SVDQ_ERR_DTYPE;
+  if (K <= 0 || K % 16 != 0) return SVDQ_ERR_SHAPE;
+  if (smooth == nullptr || smooth_table == nullptr) return SVDQ_ERR_NULL;
+  if (!aligned16(smooth_table)) return SVDQ_ERR_ALIGN;
+  return launch_smooth_table(smooth, smooth_table, K, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int svdq_quantize_w4a4_act_fuse_lora(const void* x, const void* lora_down, const void* smooth,
+                                     const void* smooth_table, void* act,
                                      void* ascales, float* lora_act, void* ascales_swz, void* lora_act16, int M,
                                      int K, int R, int M_pad, int dtype, int flags, void* stream) {
   if (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16) return SVDQ_ERR_DTYPE;
@@ -53,15 +62,17 @@ int svdq_quantize_w4a4_act_fuse_lora(const void* x, const void* lora_down, const
   if (act == nullptr || ascales == nullptr || (M > 0 && x == nullptr)) return SVDQ_ERR_NULL;
   if (R > 0 && (lora_down == nullptr || lora_act == nullptr)) return SVDQ_ERR_NULL;
   if (!aligned16(x) || !aligned16(act) || !aligned16(smooth) || !aligned16(lora_down) || !aligned16(lora_act) ||
-      !aligned16(ascales_swz) || !aligned16(lora_act16))
+      !aligned16(ascales_swz) || !aligned16(lora_act16) || !aligned16(smooth_table))
     return SVDQ_ERR_ALIGN;
+  if (smooth == nullptr && smooth_table != nullptr) return SVDQ_ERR_NULL;
   if (ascales_swz != nullptr && (M_pad % 128 != 0 || K % 64 != 0)) return SVDQ_ERR_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const bool fused_ok = M > 0 && quantize_fused_supported(M, K, R, M_pad);
+  // the fused kernel reads {smooth, 1/smooth} from the prepared table; without one it cannot smooth
+  const bool fused_ok = M > 0 && quantize_fused_supported(M, K, R, M_pad) && (smooth == nullptr || smooth_table != nullptr);
   if (flags == SVDQ_QUANT_FORCE_FUSED && !fused_ok) return SVDQ_ERR_UNSUPPORTED;
   if (fused_ok && flags != SVDQ_QUANT_FORCE_GENERIC)
-    return launch_quantize_fused(x, lora_down, smooth, act, ascales, lora_act, ascales_swz, lora_act16, M, K, R, M_pad,
-                                 dtype, st);
+    return launch_quantize_fused(x, lora_down, smooth_table, act, ascales, lora_act, ascales_swz, lora_act16, M, K, R,
+                                 M_pad, dtype, st);
   int rc = launch_quantize_rows(x, smooth, act, ascales, ascales_swz, M, M_pad, K, dtype, st);
   if (rc != SVDQ_OK) return rc;
   return launch_lora_down(x, lora_down, lora_act, lora_act16, M, M_pad, K, R, dtype, st);
@@ -132,7 +143,7 @@ struct svdq_linear_plan {
   cudaStream_t stream;
   void *x, *act, *ascales, *ascales_swz, *lora_act16, *y;       // per-call device buffers
   float* lora_act;
-  void *wgt, *wscales_swz, *lora_down, *lora_up, *smooth, *wc, *bias;  // resident weights
+  void *wgt, *wscales_swz, *lora_down, *lora_up, *smooth, *smooth_table, *wc, *bias;  // resident weights
   void *x_pin, *y_pin;                                           // pinned staging
 };
 
@@ -169,7 +180,7 @@ int svdq_linear_plan_create(svdq_linear_plan** out, int max_M, int K, int N, int
   bad = bad || cudaMalloc(&p->ascales, mp * K / 16) != cudaSuccess;
   bad = bad || cudaMalloc(&p->ascales_swz, mp * K / 16) != cudaSuccess;
   bad = bad || cudaMalloc(&p->lora_act, mp * (R > 0 ? R : 1) * 4) != cudaSuccess;
-  bad = bad || cudaMalloc(&p->lora_act16, mp * (R > 0 ? R : 1) * 2) != cudaSuccess;
+  bad = bad || cudaMalloc(&p->lora_act16, mp * (R > 0 ? R : 1) * 4) != cudaSuccess;   // bf16 keeps two planes
   bad = bad || cudaMalloc(&p->y, mp * N * 2) != cudaSuccess;
   bad = bad || cudaMallocHost(&p->x_pin, static_cast<size_t>(max_M) * K * 2) != cudaSuccess;
   bad = bad || cudaMallocHost(&p->y_pin, mp * N * 2) != cudaSuccess;
@@ -182,6 +193,10 @@ int svdq_linear_plan_create(svdq_linear_plan** out, int max_M, int K, int N, int
   if (rc == SVDQ_OK) rc = dev_upload(&p->lora_down, lora_down_host, static_cast<size_t>(K) * R * 2, p->stream);
   if (rc == SVDQ_OK) rc = dev_upload(&p->lora_up, lora_up_host, static_cast<size_t>(N) * R * 2, p->stream);
   if (rc == SVDQ_OK) rc = dev_upload(&p->smooth, smooth_host, static_cast<size_t>(K) * 2, p->stream);
+  if (rc == SVDQ_OK && p->smooth != nullptr) {
+    if (cudaMalloc(&p->smooth_table, static_cast<size_t>(K) * 8 + 16) != cudaSuccess) rc = SVDQ_ERR_CUDA;
+    if (rc == SVDQ_OK) rc = launch_smooth_table(p->smooth, p->smooth_table, K, dtype, p->stream);
+  }
   if (rc == SVDQ_OK) rc = dev_upload(&p->wc, wcscales_host, static_cast<size_t>(N) * 2, p->stream);
   if (rc == SVDQ_OK) rc = dev_upload(&p->bias, bias_host, static_cast<size_t>(N) * 2, p->stream);
   if (rc == SVDQ_OK && cudaStreamSynchronize(p->stream) != cudaSuccess) rc = SVDQ_ERR_CUDA;
@@ -204,7 +219,7 @@ int svdq_linear_plan_forward_host(svdq_linear_plan* p, const void* x_host, void*
   const void* x_src = x_host;
   if (!x_pinned) { memcpy(p->x_pin, x_host, xbytes); x_src = p->x_pin; }
   if (cudaMemcpyAsync(p->x, x_src, xbytes, cudaMemcpyHostToDevice, p->stream) != cudaSuccess) return SVDQ_ERR_CUDA;
-  int rc = svdq_quantize_w4a4_act_fuse_lora(p->x, p->lora_down, p->smooth, p->act, p->ascales, p->lora_act,
+  int rc = svdq_quantize_w4a4_act_fuse_lora(p->x, p->lora_down, p->smooth, p->smooth_table, p->act, p->ascales, p->lora_act,
                                             p->ascales_swz, p->lora_act16, M, p->K, p->R, M_pad, p->dtype,
                                             SVDQ_QUANT_AUTO, p->stream);
   if (rc != SVDQ_OK) return rc;
@@ -222,7 +237,7 @@ int svdq_linear_plan_forward_host(svdq_linear_plan* p, const void* x_host, void*
 void svdq_linear_plan_destroy(svdq_linear_plan* p) {
   if (p == nullptr) return;
   void* dev[] = {p->x, p->act, p->ascales, p->ascales_swz, p->lora_act, p->lora_act16, p->y, p->wgt,
-                 p->wscales_swz, p->lora_down, p->lora_up, p->smooth, p->wc, p->bias};
+                 p->wscales_swz, p->lora_down, p->lora_up, p->smooth, p->smooth_table, p->wc, p->bias};
   for (void* d : dev)
     if (d != nullptr) cudaFree(d);
   if (p->x_pin != nullptr) cudaFreeHost(p->x_pin);

@@ -9,56 +9,90 @@
 // The reference's own kernel for this op is
 // cute_kernels/gemm_w4a4/kernel_v2_fa4.py:841-1589.
 //
-// Work decomposition (one CTA per SM, 192 threads):
-//   warps 0-3  epilogue: tensor memory -> registers -> affine -> 16-bit -> global
-//   warp  4    producer: TMA loads into a ring of shared-memory stages
-//   warp  5    MMA issuer: scale copies smem->TMEM, tcgen05.mma, commits
-// A stage holds one 256-element K slab: A 128 x 128 B, B BN x 128 B (both
+// Work decomposition (352 threads per CTA, one CTA per SM):
+//   warps 0-7  epilogue: tensor memory -> registers -> affine -> 16 bit ->
+//              swizzled shared memory -> TMA store (a 32-row x BN/2 strip per warp)
+//   warp  8    producer: TMA loads into a ring of shared-memory stages
+//   warp  9    MMA issuer: tcgen05.mma + commits
+//   warp  10   scale copier: tcgen05.cp of the stage's scale atoms into a
+//              double-buffered scale area of tensor memory, one slab ahead
+// Issuing one tcgen05 instruction costs tens of cycles of a single thread, and a
+// 256-wide slab needs 12 scale copies next to its 4 MMAs, so the two kinds are
+// issued by different warps and handshake through mbarriers.  All three
+// single-lane roles stay converged and elect one lane per instruction, so
+// descriptors and addresses live in uniform registers.
+//
+// CG = 1: a CTA computes a 128 x BN tile.
+// CG = 2: two CTAs of a cluster compute a 256 x BN tile with cta_group::2
+//         MMAs.  Each CTA loads its own 128 rows of A and its own BN/2 rows of
+//         B (nothing is fetched twice), its own activation scales, and the
+//         weight scales of all BN columns.  Loads of both CTAs complete on the
+//         leader's "full" barrier; the leader issues the MMAs and its commits
+//         arrive on the barriers of both CTAs.
+//
+// A stage holds one 256-element K slab: A 128 x 128 B, B rows x 128 B (both
 // 128-byte swizzled, K-major, two E2M1 codes per byte) and their scale atoms.
 // The LoRA-up product reuses the very same ring: a slab of 64 rank elements of
-// lora_act (128 rows x 128 B) and lora_up (BN rows x 128 B) has exactly the
-// byte footprint of a main slab, so it is just ceil(R/64) more ring passes per
-// output tile, issued as dense 16-bit MMAs into the same accumulator.
+// lora_act (128 rows x 128 B) and lora_up (B rows x 128 B) has exactly the byte
+// footprint of a main slab, so it is ceil(R/64) more ring passes per output
+// tile, issued as dense 16-bit MMAs into the same accumulator.  Both operands
+// of a dense MMA must have the same 16-bit format (an fp16 x bf16 pair is an
+// illegal instruction on this part), so lora_act arrives in the output type:
+// fp16 as one rounded copy, bf16 as a hi + lo pair (lora_act = hi + lo to 16
+// significant bits) that takes two passes over the same lora_up slab - a single
+// bf16 copy would put the LoRA term's 2^-9 rounding error above the 1e-3 bound.
 #include "sm100.cuh"
 #include "svdq_internal.h"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
-#include <type_traits>
 #include <cstdlib>
+#include <type_traits>
 
 namespace svdq {
 
 namespace gemm {
 
-constexpr int BM = 128;          // rows of y per CTA tile
+constexpr int BM = 128;          // rows of y per CTA
 constexpr int BK = 256;          // K elements per stage (128 bytes of codes per row)
 constexpr int A_BYTES = BM * 128;
 constexpr int SFA_BYTES = BM * (BK / 16);  // 2048
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int NUM_THREADS = (EPI_WARPS + 3) * 32;
+constexpr int STORE_BUF_BYTES = 32 * 128;  // one 32-row x 64-column strip of y
 
-template <int BN>
+template <int CG, int BN>
 struct Cfg {
-  static constexpr int B_BYTES = BN * 128;
+  static constexpr int B_ROWS = BN / CG;                           // rows of B this CTA loads
+  static constexpr int B_BYTES = B_ROWS * 128;
   static constexpr int SFB_BYTES = BN * (BK / 16);
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int ACC_STAGES = (BN <= 128) ? 2 : 1;
-  static constexpr int STAGES = (BN <= 128) ? 6 : 4;
+  // Staging strips per epilogue warp.  With a whole tile of strips the accumulator is drained at
+  // register speed and released while the TMA stores are still in flight; a single CTA with a
+  // 256-wide tile cannot afford that next to three 54 KB ring stages and keeps two.
+  static constexpr int GROUPS_PER_WARP = BN / 128;                 // 64-column strips each epilogue warp handles per tile
+  static constexpr int STORE_BUFS = (CG == 1 && BN == 256) ? 1 : GROUPS_PER_WARP;
+  static constexpr int STORE_BYTES = EPI_WARPS * STORE_BUFS * STORE_BUF_BYTES;
+  static constexpr int TAIL_BYTES = 2048 /*affine*/ + 256 /*barriers*/;
+  static constexpr int STAGES_RAW = (232448 - 1024 - STORE_BYTES - TAIL_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SFA_COLS = 16;                 // 4 k-blocks x 4 columns
   static constexpr int SFB_COLS = 4 * (BN / 32);      // 4 k-blocks x BN/32 columns
+  static constexpr int SF_COLS = SFA_COLS + SFB_COLS; // one scale buffer; two are kept
   static constexpr int TMEM_COLS = 512;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 2048 /*affine*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STORE_BYTES + TAIL_BYTES;
+  static_assert(ACC_STAGES * BN + 2 * SF_COLS <= TMEM_COLS, "tensor memory budget");
+  static_assert(STAGES >= 3, "ring too shallow");
+  static_assert((2 * STAGES + 2 * ACC_STAGES + 4) * 8 + 16 <= 256, "barrier block");
 };
 
 struct Params {
-  const uint8_t* sfa;   // swizzled activation scales
-  const uint8_t* sfb;   // swizzled weight scales
   const void* wc;       // [N] or null
   const void* bias;     // [N] or null
-  void* y;              // [M, N]
   int M, N, K, R;
-  int tiles_m, tiles_n;
-  int dbg;   // TEMP diagnostic switches
+  int tiles_m, tiles_n; // in units of (CG*128) x BN
+  int dbg;              // TEMP diagnostic switches
 };
 
 __device__ __forceinline__ uint32_t pack2(__half a, __half b) {
@@ -69,6 +103,15 @@ __device__ __forceinline__ uint32_t pack2(__nv_bfloat16 a, __nv_bfloat16 b) {
   __nv_bfloat162 h = __halves2bfloat162(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
 }
+template <typename T> __device__ __forceinline__ uint32_t pack2f(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2f<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2f<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
 template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
@@ -76,192 +119,287 @@ template <typename T> __device__ __forceinline__ float as_f32(T v);
 template <> __device__ __forceinline__ float as_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float as_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-template <int BN, typename OutT>
+template <int CG, int BN, typename OutT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmLA, const __grid_constant__ CUtensorMap tmLU, const Params p) {
-  using C = Cfg<BN>;
-  constexpr bool kBf16 = sizeof(OutT) == 2 && !std::is_same<OutT, __half>::value;
+                 const __grid_constant__ CUtensorMap tmLA, const __grid_constant__ CUtensorMap tmLU,
+                 const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmSFA,
+                 const __grid_constant__ CUtensorMap tmSFB, const Params p) {
+  using C = Cfg<CG, BN>;
+  constexpr bool kBf16 = std::is_same<OutT, __nv_bfloat16>::value;
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* tail = smem + C::STAGES * C::STAGE_BYTES;
+  // 1 KB alignment by pointer arithmetic (not an integer round trip) so that the compiler keeps
+  // the shared address space and emits shared-memory loads and stores
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint8_t* store_bufs = smem + C::STAGES * C::STAGE_BYTES;        // 1024-aligned: every stage is a multiple of 1 KB
+  uint8_t* tail = store_bufs + C::STORE_BYTES;
   float* affine = reinterpret_cast<float*>(tail);                 // [2][BN] : wcscales, bias of the current tile
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2048);
-  uint64_t* full = bars;                                          // [STAGES]
-  uint64_t* empty = bars + C::STAGES;                             // [STAGES]
-  uint64_t* acc_full = bars + 2 * C::STAGES;                      // [ACC_STAGES]
-  uint64_t* acc_empty = acc_full + C::ACC_STAGES;                 // [ACC_STAGES]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::ACC_STAGES);
+  uint64_t* full = bars;                                          // [STAGES]     loads landed (leader CTA's copy is used)
+  uint64_t* empty = bars + C::STAGES;                             // [STAGES]     stage consumed by the MMAs (per CTA)
+  uint64_t* acc_full = bars + 2 * C::STAGES;                      // [ACC_STAGES] accumulator complete (per CTA)
+  uint64_t* acc_empty = acc_full + C::ACC_STAGES;                 // [ACC_STAGES] accumulator drained (leader's copy is used)
+  uint64_t* sf_full = acc_empty + C::ACC_STAGES;                  // [2] scale buffer copied (leader CTA)
+  uint64_t* sf_empty = sf_full + 2;                               // [2] scale buffer consumed by the MMAs (leader CTA)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx ctx{abort_flag};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;      // 0 = leader of the pair
+  const int pair = blockIdx.x / CG;
+  const int num_pairs = gridDim.x / CG;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < C::ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 4); }
+    for (int a = 0; a < C::ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EPI_WARPS * CG); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&sf_full[b], 1); mbar_init(&sf_empty[b], 1); }
     fence_barrier_init();
   }
-  if (warp == 4 && lane == 0) {
-    tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB);
+  if (warp == EPI_WARPS && lane == 0) {
+    tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmY);
+    tma_prefetch_desc(&tmSFA); tma_prefetch_desc(&tmSFB);
     if (p.R > 0) { tma_prefetch_desc(&tmLA); tma_prefetch_desc(&tmLU); }
   }
-  if (warp == 5) {
-    tmem_alloc(tmem_slot, C::TMEM_COLS);
-    tmem_relinquish();
+  if (warp == EPI_WARPS + 1) {
+    if constexpr (CG == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+    else { tmem_alloc_pair(tmem_slot, C::TMEM_COLS); tmem_relinquish_pair(); }
   }
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();   // both CTAs' barriers exist before anything remote touches them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_sfa = tmem_base + C::ACC_STAGES * BN;
-  const uint32_t tmem_sfb = tmem_sfa + C::SFA_COLS;
+  const uint32_t tmem_sf = tmem_base + C::ACC_STAGES * BN;       // two buffers of [SFA 16 | SFB] columns
 
   const int kt_main = (p.K + BK - 1) / BK;   // the last slab may hold fewer than four 64-element k-blocks
-  const int kt_lora = (p.R + 63) / 64;
+  constexpr int kLoraParts = kBf16 ? 2 : 1;        // bf16: hi and lo halves of lora_act
+  const int lora_slabs = (p.R + 63) / 64;
+  const int kt_lora = kLoraParts * lora_slabs;
   const int kt_all = kt_main + kt_lora;
   const int total_tiles = p.tiles_m * p.tiles_n;
-  const int k_groups4 = p.K / 64;   // scale atoms along K
+  const int k_groups4 = p.K / 64;            // scale atoms along K
 
-  if (warp == 4) {
-    // ------------------------------ producer ------------------------------
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int mb = tile % p.tiles_m, nb = tile / p.tiles_m;
-        const int m0 = mb * BM, n0 = nb * BN;
-        for (int kt = 0; kt < kt_all; ++kt, ++it) {
-          const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
-          if (!mbar_wait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, it)) { ok = false; break; }
-          uint8_t* st = smem + s * C::STAGE_BYTES;
-          if (p.dbg & 8) { mbar_arrive(&full[s]); continue; }
-          if (kt < kt_main) {
-            // codes past K are zero-filled by TMA (and still counted); scale atoms past K are not fetched
-            const uint32_t nkb = min(4, k_groups4 - kt * 4);
-            mbar_arrive_expect_tx(&full[s], A_BYTES + C::B_BYTES + nkb * 512u * (1 + BN / 128));
-            tma_load_2d(st, &tmA, kt * 128, m0, &full[s]);
-            tma_load_2d(st + A_BYTES, &tmB, kt * 128, n0, &full[s]);
-            bulk_load_1d(st + A_BYTES + C::B_BYTES, p.sfa + (static_cast<size_t>(mb) * k_groups4 + kt * 4) * 512, nkb * 512u, &full[s]);
-#pragma unroll
-            for (int h = 0; h < BN / 128; ++h)
-              bulk_load_1d(st + A_BYTES + C::B_BYTES + SFA_BYTES + h * 2048,
-                           p.sfb + (static_cast<size_t>(nb * (BN / 128) + h) * k_groups4 + kt * 4) * 512, nkb * 512u, &full[s]);
+  if (warp == EPI_WARPS) {
+    // ------------------------------ producer (both CTAs) ------------------------------
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+      const int mb = tile % p.tiles_m, nb = tile / p.tiles_m;
+      const int m0 = (mb * CG + rank) * BM;
+      const int n0 = nb * BN;
+      const int nrow0 = n0 + rank * C::B_ROWS;
+      for (int kt = 0; kt < kt_all; ++kt, ++it) {
+        const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, it)) { ok = false; break; }
+        uint8_t* st = smem + s * C::STAGE_BYTES;
+        // Codes past K are zero-filled by TMA.  The scale atoms of a (128-row block, slab) are four
+        // consecutive 512-byte rows of the swizzled scale buffer seen as a [blocks * K/64, 512 B] matrix;
+        // a short last slab just fetches (and never uses) the rows that follow.  Every byte of a box
+        // counts toward the barrier whether it was in bounds or not.
+        const uint32_t my_bytes = kt < kt_main ? C::STAGE_BYTES : A_BYTES + C::B_BYTES;
+        // the barrier that counts this CTA's bytes: its own for CG = 1, the leader's for a pair
+        const uint32_t bar = (CG == 2) ? map_to_cta(smem_u32(&full[s]), 0) : smem_u32(&full[s]);
+        if (elect_one()) {
+          if (p.dbg & 8) {
+            if (rank == 0) mbar_arrive(&full[s]);
           } else {
-            const int r0 = (kt - kt_main) * 64;
-            mbar_arrive_expect_tx(&full[s], A_BYTES + C::B_BYTES);
-            tma_load_2d(st, &tmLA, r0, m0, &full[s]);
-            tma_load_2d(st + A_BYTES, &tmLU, r0, n0, &full[s]);
+            if (rank == 0) mbar_arrive_expect_tx(&full[s], my_bytes * CG);
+            if (kt < kt_main) {
+              tma_load_2d_bar<CG>(st, &tmA, kt * 128, m0, bar);
+              tma_load_2d_bar<CG>(st + A_BYTES, &tmB, kt * 128, nrow0, bar);
+              tma_load_2d_bar<CG>(st + A_BYTES + C::B_BYTES, &tmSFA, 0, (mb * CG + rank) * k_groups4 + kt * 4, bar);
+#pragma unroll
+              for (int h = 0; h < BN / 128; ++h)
+                tma_load_2d_bar<CG>(st + A_BYTES + C::B_BYTES + SFA_BYTES + h * 2048, &tmSFB, 0,
+                                    (nb * (BN / 128) + h) * k_groups4 + kt * 4, bar);
+            } else {
+              const int lt = kt - kt_main;
+              const int part = lt / lora_slabs, r0 = (lt % lora_slabs) * 64;
+              tma_load_2d_bar<CG>(st, &tmLA, r0, part * p.M + m0, bar);      // lora_act parts are stacked along rows
+              tma_load_2d_bar<CG>(st + A_BYTES, &tmLU, r0, nrow0, bar);
+            }
           }
         }
+        __syncwarp();
       }
     }
-    __syncwarp();
-  } else if (warp == 5) {
-    // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+  } else if (warp == EPI_WARPS + 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    if (rank == 0) {
       constexpr uint64_t kDescAB = smem_desc_base(0, 1024, kSwizzle128B);   // K-major, 8-row groups 1024 B apart
-      constexpr uint64_t kDescSF = smem_desc_base(0, 128, kSwizzleNone);    // 8 x 16 B core matrices, 128 B apart
-      constexpr uint32_t kIdescMain = idesc_nvfp4(BM, BN);
-      constexpr uint32_t kIdescLora = idesc_f16(kBf16, BM, BN, false, false);
-      uint32_t it = 0, tcount = 0;
+      constexpr uint32_t kIdescMain = idesc_nvfp4(BM * CG, BN);
+      constexpr uint32_t kIdescLora = idesc_f16(kBf16, kBf16, BM * CG, BN, false, false);
+      constexpr uint16_t kMask = (CG == 2) ? 3 : 1;
+      uint32_t it = 0, tcount = 0, sf_it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++tcount) {
         const uint32_t as = tcount % C::ACC_STAGES, aph = (tcount / C::ACC_STAGES) & 1;
-        if (!mbar_wait(&acc_empty[as], aph ^ 1, ctx, kDevWaitAccFree, tcount)) { ok = false; break; }
+        if (!(p.dbg & 32) && !mbar_wait(&acc_empty[as], aph ^ 1, ctx, kDevWaitAccFree, tcount)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + as * BN;
         for (int kt = 0; kt < kt_all; ++kt, ++it) {
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
           if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, it)) { ok = false; break; }
+          const bool main_slab = kt < kt_main;
+          const uint32_t sb = sf_it & 1;
+          if (main_slab && !(p.dbg & 4)) {
+            if (!mbar_wait(&sf_full[sb], (sf_it >> 1) & 1, ctx, kDevWaitMisc, it)) { ok = false; break; }
+          }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
-          if (kt < kt_main) {
-            const uint32_t sfa_addr = b_addr + C::B_BYTES;
-            const uint32_t sfb_addr = sfa_addr + SFA_BYTES;
-            const int nkb = (p.dbg & 4) ? 0 : min(4, k_groups4 - kt * 4);
+          const uint32_t tsfa = tmem_sf + sb * C::SF_COLS, tsfb = tsfa + C::SFA_COLS;
+          const int nkb = (p.dbg & 4) ? 0 : (main_slab ? min(4, k_groups4 - kt * 4)
+                                                        : min(4, (p.R - ((kt - kt_main) % lora_slabs) * 64) / 16));
+          if (elect_one()) {
+            if (main_slab) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (j < nkb)
+                  mma_nvfp4<CG>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
+                                kIdescMain, tsfa + j * 4, tsfb + j * (BN / 32), (kt | j) != 0 ? 1u : 0u);
+              if (!(p.dbg & 4)) tc_commit_local<CG>(&sf_empty[sb]);   // scale buffer reusable once these MMAs are done
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (j < nkb)
+                  mma_f16<CG>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
+                              kIdescLora, (kt | j) != 0 ? 1u : 0u);
+            }
+            tc_commit_mask<CG>(&empty[s], kMask);          // stage reusable (in both CTAs) once these MMAs have read it
+            if (kt == kt_all - 1) tc_commit_mask<CG>(&acc_full[as], kMask);   // accumulator complete
+          }
+          __syncwarp();
+          if (main_slab) ++sf_it;
+        }
+      }
+    }
+  } else if (warp == EPI_WARPS + 2) {
+    // ------------------------------ scale copier (leader CTA only) ------------------------------
+    // Copies the scale atoms of main slab n into scale buffer n % 2 while the MMAs of slab n - 1 run.
+    if (rank == 0 && !(p.dbg & 4)) {
+      constexpr uint64_t kDescSF = smem_desc_base(0, 128, kSwizzleNone);    // 8 x 16 B core matrices, 128 B apart
+      uint32_t it = 0, sf_it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+        for (int kt = 0; kt < kt_all; ++kt, ++it) {
+          if (kt >= kt_main) continue;                      // LoRA slabs carry no scales
+          const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
+          const uint32_t sb = sf_it & 1;
+          if (!mbar_wait(&sf_empty[sb], ((sf_it >> 1) & 1) ^ 1, ctx, kDevWaitMisc, 0x20000 + it)) { ok = false; break; }
+          if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, 0x20000 + it)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sfa_addr = smem_u32(smem + s * C::STAGE_BYTES) + A_BYTES + C::B_BYTES;
+          const uint32_t sfb_addr = sfa_addr + SFA_BYTES;
+          const uint32_t tsfa = tmem_sf + sb * C::SF_COLS, tsfb = tsfa + C::SFA_COLS;
+          const int nkb = min(4, k_groups4 - kt * 4);
+          if (elect_one()) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               if (j < nkb && !((p.dbg & 2) && kt > 0)) {
-                tmem_cp_scales<1>(tmem_sfa + j * 4, smem_desc(kDescSF, sfa_addr + j * 512));
+                tmem_cp_scales<CG>(tsfa + j * 4, smem_desc(kDescSF, sfa_addr + j * 512));
 #pragma unroll
                 for (int h = 0; h < BN / 128; ++h)
-                  tmem_cp_scales<1>(tmem_sfb + j * (BN / 32) + h * 4, smem_desc(kDescSF, sfb_addr + h * 2048 + j * 512));
+                  tmem_cp_scales<CG>(tsfb + j * (BN / 32) + h * 4, smem_desc(kDescSF, sfb_addr + h * 2048 + j * 512));
               }
             }
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (j < nkb) mma_nvfp4<1>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
-                           kIdescMain, tmem_sfa + j * 4, tmem_sfb + j * (BN / 32), (kt | j) != 0 ? 1u : 0u);
-          } else {
-            const int r0 = (kt - kt_main) * 64;
-            const int nk = (p.dbg & 4) ? 0 : min(4, (p.R - r0) / 16);
-            for (int j = 0; j < nk; ++j)
-              mma_f16<1>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
-                         kIdescLora, (kt | j) != 0 ? 1u : 0u);
+            tc_commit_local<CG>(&sf_full[sb]);
           }
-          tc_commit(&empty[s]);          // stage reusable once these MMAs have read it
+          __syncwarp();
+          ++sf_it;
         }
-        if (ok) tc_commit(&acc_full[as]);  // accumulator complete
       }
     }
-    __syncwarp();
   } else {
-    // ------------------------------ epilogue (warps 0-3) ------------------------------
-    OutT* y = static_cast<OutT*>(p.y);
+    // ------------------------------ epilogue (warps 0-7, both CTAs) ------------------------------
+    // Warp w drains the 32 accumulator rows of lane quarter w % 4 and the column half w / 4.
     const OutT* wc = static_cast<const OutT*>(p.wc);
     const OutT* bias = static_cast<const OutT*>(p.bias);
-    uint32_t tcount = 0;
+    const int quarter = warp & 3, chalf = warp >> 2;
+    uint8_t* my_bufs = store_bufs + warp * (C::STORE_BUFS * STORE_BUF_BYTES);
+    const uint32_t swz = static_cast<uint32_t>(lane & 7);
+    uint32_t tcount = 0, nstore = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tcount) {
+    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++tcount) {
       const int mb = tile % p.tiles_m, nb = tile / p.tiles_m;
-      const int m0 = mb * BM, n0 = nb * BN;
+      const int m0 = (mb * CG + rank) * BM, n0 = nb * BN;
       const uint32_t as = tcount % C::ACC_STAGES, aph = (tcount / C::ACC_STAGES) & 1;
-      // stage this tile's per-column affine terms (previous tile's readers are done: see the barrier below)
-      for (int c = threadIdx.x; c < BN; c += 128) {
+      // stage this tile's per-column affine terms (the previous tile's readers are past the barrier below)
+      for (int c = threadIdx.x; c < BN; c += EPI_WARPS * 32) {
         affine[c] = wc != nullptr ? as_f32<OutT>(wc[n0 + c]) : 1.0f;
         affine[BN + c] = bias != nullptr ? as_f32<OutT>(bias[n0 + c]) : 0.0f;
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
       if (!mbar_wait(&acc_full[as], aph, ctx, kDevWaitAcc, tcount)) ok = false;
       tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + as * BN;
-      const size_t row = static_cast<size_t>(m0 + warp * 32 + lane);
-      OutT* yrow = y + row * p.N + n0;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN + chalf * (BN / 2);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(taddr + c0, v);
+      for (int g = 0; g < C::GROUPS_PER_WARP; ++g, ++nstore) {
+        uint8_t* buf = my_bufs + (nstore % C::STORE_BUFS) * STORE_BUF_BYTES;
+        // the TMA store that last read this buffer must be done with it
+        if (lane == 0) tma_store_wait_read<C::STORE_BUFS - 1>();
+        __syncwarp();
+        uint32_t v[2][32];
+        tmem_ld_32x32(taddr + g * 64, v[0]);
+        tmem_ld_32x32(taddr + g * 64 + 32, v[1]);
         tmem_ld_wait();
-        uint32_t o[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float a = __uint_as_float(v[2 * i]), b = __uint_as_float(v[2 * i + 1]);
-          if (wc != nullptr) { a = __fmul_rn(a, affine[c0 + 2 * i]); b = __fmul_rn(b, affine[c0 + 2 * i + 1]); }
-          if (bias != nullptr) { a = __fadd_rn(a, affine[BN + c0 + 2 * i]); b = __fadd_rn(b, affine[BN + c0 + 2 * i + 1]); }
-          o[i] = pack2(from_f32<OutT>(a), from_f32<OutT>(b));
+        if (g == C::GROUPS_PER_WARP - 1) {
+          // every column this warp owns has left tensor memory
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (CG == 2) mbar_arrive_cluster(&acc_empty[as], 0); else mbar_arrive(&acc_empty[as]);
+          }
         }
-        uint4* dst = reinterpret_cast<uint4*>(yrow + c0);
-        if (!(p.dbg & 1)) {
+        const int cbase = chalf * (BN / 2) + g * 64;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) dst[i] = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+        for (int hc = 0; hc < 2; ++hc) {
+          const float4* wc4 = reinterpret_cast<const float4*>(affine + cbase + hc * 32);
+          const float4* bs4 = reinterpret_cast<const float4*>(affine + BN + cbase + hc * 32);
+          uint32_t o[16];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float a0 = __uint_as_float(v[hc][4 * i]), a1 = __uint_as_float(v[hc][4 * i + 1]);
+            float a2 = __uint_as_float(v[hc][4 * i + 2]), a3 = __uint_as_float(v[hc][4 * i + 3]);
+            if (wc != nullptr) {
+              const float4 w4 = wc4[i];
+              a0 = __fmul_rn(a0, w4.x); a1 = __fmul_rn(a1, w4.y); a2 = __fmul_rn(a2, w4.z); a3 = __fmul_rn(a3, w4.w);
+            }
+            if (bias != nullptr) {
+              const float4 b4 = bs4[i];
+              a0 = __fadd_rn(a0, b4.x); a1 = __fadd_rn(a1, b4.y); a2 = __fadd_rn(a2, b4.z); a3 = __fadd_rn(a3, b4.w);
+            }
+            o[2 * i] = pack2f<OutT>(a0, a1);
+            o[2 * i + 1] = pack2f<OutT>(a2, a3);
+          }
+          // row `lane` of the strip: 16-byte chunks hc*4 .. hc*4+3, XOR-swizzled like the TMA box
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint32_t chunk = static_cast<uint32_t>(hc * 4 + i) ^ swz;
+            *reinterpret_cast<uint4*>(buf + lane * 128 + chunk * 16) = make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && !(p.dbg & 1)) {
+          tma_store_2d(&tmY, buf, n0 + cbase, m0 + quarter * 32);
+          tma_store_commit();
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[as]);
-      // affine[] may be overwritten after this barrier; it also makes the four warps agree on whether to go on
+      // affine[] may be overwritten after this barrier; it also makes the eight warps agree on whether to go on
       uint32_t any_failed;
       asm volatile(
           "{\n\t.reg .pred p, q;\n\tsetp.eq.u32 p, %1, 0;\n\t"
-          "bar.red.or.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-          : "=r"(any_failed) : "r"(ok ? 1u : 0u) : "memory");
+          "bar.red.or.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+          : "=r"(any_failed) : "r"(ok ? 1u : 0u), "n"(EPI_WARPS * 32) : "memory");
       ok = any_failed == 0;
     }
+    if (lane == 0) tma_store_wait_all<0>();   // global writes of this warp are complete before the CTA ends
+    __syncwarp();
   }
 
   // ------------------------------ teardown ------------------------------
@@ -273,9 +411,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     while (globaltimer_ns() - t0 < 50000ull) { __nanosleep(1000); }
     __syncthreads();
   }
-  if (warp == 5) {
+  if constexpr (CG == 2) cluster_sync_all();   // the partner may still read this CTA's shared memory / signal its barriers
+  if (warp == EPI_WARPS + 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if constexpr (CG == 1) tmem_dealloc(tmem_base, C::TMEM_COLS); else tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -285,53 +424,88 @@ bool gemm_supported(int M, int N, int K, int R) {
   return M > 0 && N > 0 && K > 0 && M % 128 == 0 && N % 128 == 0 && K % 64 == 0 && R >= 0 && R % 16 == 0;
 }
 
-template <int BN, typename OutT>
+template <int CG, int BN, typename OutT>
 static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, const void* sfb, const void* la,
                          const void* lu, const void* wc, const void* bias, void* y, int M, int N, int K, int R,
                          cudaStream_t stream) {
-  using C = gemm::Cfg<BN>;
-  CUtensorMap tmA, tmB, tmLA, tmLU;
+  using C = gemm::Cfg<CG, BN>;
+  CUtensorMap tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB;
   int rc;
+  const uint64_t atoms_k = K / 64;
+  if ((rc = make_tmap_2d(&tmSFA, sfa, 4, (M / 128) * atoms_k, 128, 512, 4, 128, kTmapSwizzleNone)) != SVDQ_OK) return rc;
+  if ((rc = make_tmap_2d(&tmSFB, sfb, 4, (N / 128) * atoms_k, 128, 512, 4, 128, kTmapSwizzleNone)) != SVDQ_OK) return rc;
   if ((rc = make_tmap_2d(&tmA, act, 1, M, K / 2, K / 2, gemm::BM, 128, kTmapSwizzle128)) != SVDQ_OK) return rc;
-  if ((rc = make_tmap_2d(&tmB, wgt, 1, N, K / 2, K / 2, BN, 128, kTmapSwizzle128)) != SVDQ_OK) return rc;
+  if ((rc = make_tmap_2d(&tmB, wgt, 1, N, K / 2, K / 2, C::B_ROWS, 128, kTmapSwizzle128)) != SVDQ_OK) return rc;
+  if ((rc = make_tmap_2d(&tmY, y, 2, M, N, static_cast<uint64_t>(N) * 2, 32, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
   if (R > 0) {
-    if ((rc = make_tmap_2d(&tmLA, la, 2, M, R, static_cast<uint64_t>(R) * 2, gemm::BM, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
-    if ((rc = make_tmap_2d(&tmLU, lu, 2, N, R, static_cast<uint64_t>(R) * 2, BN, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
+    const uint64_t la_rows = static_cast<uint64_t>(M) * (std::is_same<OutT, __nv_bfloat16>::value ? 2 : 1);
+    if ((rc = make_tmap_2d(&tmLA, la, 2, la_rows, R, static_cast<uint64_t>(R) * 2, gemm::BM, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
+    if ((rc = make_tmap_2d(&tmLU, lu, 2, N, R, static_cast<uint64_t>(R) * 2, C::B_ROWS, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
   } else {
     tmLA = tmA; tmLU = tmB;
   }
   gemm::Params p;
-  p.sfa = static_cast<const uint8_t*>(sfa);
-  p.sfb = static_cast<const uint8_t*>(sfb);
-  p.wc = wc; p.bias = bias; p.y = y;
+  p.wc = wc; p.bias = bias;
   p.M = M; p.N = N; p.K = K; p.R = R;
-  p.tiles_m = M / gemm::BM; p.tiles_n = N / BN;
+  p.tiles_m = M / (gemm::BM * CG); p.tiles_n = N / BN;
   { const char* e = getenv("SVDQ_DEBUG"); p.dbg = e ? atoi(e) : 0; }
-  auto kern = gemm::gemm_w4a4_kernel<BN, OutT>;
+  auto kern = gemm::gemm_w4a4_kernel<CG, BN, OutT>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return SVDQ_ERR_LAUNCH;
     configured = true;
   }
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  kern<<<grid, gemm::NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmLA, tmLU, p);
-  return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;
+  const int max_pairs = sm_count() / CG;
+  const int pairs = tiles < max_pairs ? tiles : max_pairs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pairs * CG, 1, 1);
+  cfg.blockDim = dim3(gemm::NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, p) != cudaSuccess) return SVDQ_ERR_LAUNCH;
+  return SVDQ_OK;
 }
 
+template <typename OutT>
+static int launch_gemm_dt(int cg, int bn, const void* act, const void* wgt, const void* sfa, const void* sfb,
+                          const void* la, const void* lu, const void* wc, const void* bias, void* y, int M, int N, int K,
+                          int R, cudaStream_t stream) {
+  if (cg == 2 && bn == 256) return launch_gemm_t<2, 256, OutT>(act, wgt, sfa, sfb, la, lu, wc, bias, y, M, N, K, R, stream);
+  if (cg == 2 && bn == 128) return launch_gemm_t<2, 128, OutT>(act, wgt, sfa, sfb, la, lu, wc, bias, y, M, N, K, R, stream);
+  if (cg == 1 && bn == 256) return launch_gemm_t<1, 256, OutT>(act, wgt, sfa, sfb, la, lu, wc, bias, y, M, N, K, R, stream);
+  return launch_gemm_t<1, 128, OutT>(act, wgt, sfa, sfb, la, lu, wc, bias, y, M, N, K, R, stream);
+}
+
+// variant: 0 = choose; 128 / 256 = one CTA per tile with that N tile; 2128 / 2256 = CTA pairs (256-row tiles)
 int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
                      const void* lora_act16, const void* lora_up, const void* wcscales, const void* bias, void* y,
                      int M, int N, int K, int R, int dtype, int variant, cudaStream_t stream) {
   if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
-  const bool wide = (variant == 0) ? (N % 256 == 0) : (variant == 256);
-  if (wide && N % 256 != 0) return SVDQ_ERR_SHAPE;
-  if (dtype == SVDQ_DTYPE_F16) {
-    return wide ? launch_gemm_t<256, __half>(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, wcscales, bias, y, M, N, K, R, stream)
-                : launch_gemm_t<128, __half>(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, wcscales, bias, y, M, N, K, R, stream);
-  } else if (dtype == SVDQ_DTYPE_BF16) {
-    return wide ? launch_gemm_t<256, __nv_bfloat16>(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, wcscales, bias, y, M, N, K, R, stream)
-                : launch_gemm_t<128, __nv_bfloat16>(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, wcscales, bias, y, M, N, K, R, stream);
+  int cg, bn;
+  if (variant == 0) {
+    const char* e = getenv("SVDQ_GEMM_VARIANT");
+    if (e) variant = atoi(e);
   }
+  if (variant == 0) {
+    cg = (M % 256 == 0) ? 2 : 1;
+    bn = (N % 256 == 0) ? 256 : 128;
+  } else if (variant == 128 || variant == 256) {
+    cg = 1; bn = variant;
+  } else {
+    cg = variant / 1000; bn = variant % 1000;
+  }
+  if ((cg != 1 && cg != 2) || (bn != 128 && bn != 256)) return SVDQ_ERR_UNSUPPORTED;
+  if (M % (128 * cg) != 0 || N % bn != 0) return SVDQ_ERR_SHAPE;
+  if (dtype == SVDQ_DTYPE_F16)
+    return launch_gemm_dt<__half>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, wcscales, bias, y, M, N, K, R, stream);
+  if (dtype == SVDQ_DTYPE_BF16)
+    return launch_gemm_dt<__nv_bfloat16>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, wcscales, bias, y, M, N, K, R, stream);
   return SVDQ_ERR_DTYPE;
 }
 

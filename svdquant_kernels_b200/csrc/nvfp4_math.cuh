@@ -70,6 +70,51 @@ __device__ __forceinline__ uint32_t e2m1_code(float v, const GroupBounds& g) {
   return idx | ((v < 0.0f) ? 8u : 0u);
 }
 
+// lora_act in the 16-bit form the GEMM's dense MMA consumes (same format as lora_up):
+//   fp16: one copy, round to nearest even, magnitudes beyond 65504 clamp to it
+//   bf16: hi = bf16(v) and lo = bf16(v - hi), stored as two [rows, R] planes; hi + lo carries
+//         16 significant bits of v with bf16's full exponent range
+__device__ __forceinline__ __half f32_to_f16_sat(float v) {
+  return __float2half_rn(fminf(fmaxf(v, -65504.0f), 65504.0f));
+}
+__device__ __forceinline__ void f32_to_bf16_hi_lo(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+  hi = __float2bfloat16_rn(v);
+  lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+// writes element `idx` (of `plane` elements per plane) of the 16-bit form of v
+template <typename T>
+__device__ __forceinline__ void store_lora16(void* base, size_t idx, size_t plane, float v);
+template <>
+__device__ __forceinline__ void store_lora16<__half>(void* base, size_t idx, size_t, float v) {
+  static_cast<__half*>(base)[idx] = f32_to_f16_sat(v);
+}
+template <>
+__device__ __forceinline__ void store_lora16<__nv_bfloat16>(void* base, size_t idx, size_t plane, float v) {
+  __nv_bfloat16 hi, lo;
+  f32_to_bf16_hi_lo(v, hi, lo);
+  static_cast<__nv_bfloat16*>(base)[idx] = hi;
+  static_cast<__nv_bfloat16*>(base)[plane + idx] = lo;
+}
+// four consecutive elements at once (idx % 4 == 0)
+template <typename T>
+__device__ __forceinline__ void store_lora16x4(void* base, size_t idx, size_t plane, float4 v);
+template <>
+__device__ __forceinline__ void store_lora16x4<__half>(void* base, size_t idx, size_t, float4 v) {
+  __half2 a = __floats2half2_rn(fminf(fmaxf(v.x, -65504.0f), 65504.0f), fminf(fmaxf(v.y, -65504.0f), 65504.0f));
+  __half2 b = __floats2half2_rn(fminf(fmaxf(v.z, -65504.0f), 65504.0f), fminf(fmaxf(v.w, -65504.0f), 65504.0f));
+  *reinterpret_cast<uint2*>(static_cast<__half*>(base) + idx) =
+      make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&b));
+}
+template <>
+__device__ __forceinline__ void store_lora16x4<__nv_bfloat16>(void* base, size_t idx, size_t plane, float4 v) {
+  __nv_bfloat162 h0 = __floats2bfloat162_rn(v.x, v.y), h1 = __floats2bfloat162_rn(v.z, v.w);
+  const float2 f0 = __bfloat1622float2(h0), f1 = __bfloat1622float2(h1);
+  __nv_bfloat162 l0 = __floats2bfloat162_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2bfloat162_rn(v.z - f1.x, v.w - f1.y);
+  __nv_bfloat16* p = static_cast<__nv_bfloat16*>(base);
+  *reinterpret_cast<uint2*>(p + idx) = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
+  *reinterpret_cast<uint2*>(p + plane + idx) = make_uint2(*reinterpret_cast<uint32_t*>(&l0), *reinterpret_cast<uint32_t*>(&l1));
+}
+
 // byte offset of (row m, group g) inside the 128-row x 4-group scale atoms the
 // tensor core reads (cute_kernels/gemm_w4a4/kernel.py:194-225 builds the same
 // order with a transpose + permute): atoms of 512 bytes ordered (m/128, g/4).

@@ -7,57 +7,67 @@
 // (triton_kernels/quantize_w4a4_act_fuse_lora/kernel.py:115-286); results
 // follow baseline/kernels/quantize_w4a4_act_fuse_lora/ref.py:19-50.
 //
-// Decomposition.  A cluster of KS CTAs owns one tile of 128 rows; CTA k of the
-// cluster owns a contiguous range of 64-column slabs of K.  Per slab the
-// producer warp TMA-loads the x tile (128 x 64, 128-byte swizzle) and the
-// matching lora_down slab (64 x R) into one ring stage.  Two consumers read
-// the same stage: the MMA warp accumulates x_tile @ lora_down_slab into a
-// [128 x R] fp32 accumulator in tensor memory, and the quantize warps turn the
-// tile into codes and scales.  x is read from HBM exactly once.  At the end the
-// KS partial accumulators are summed in a fixed order through distributed
-// shared memory (no atomics, no zero-fill, no scratch in global memory).
+// Decomposition.  A cluster of KS (1 or 2) CTAs owns one tile of 64 rows; CTA k
+// owns a contiguous range of 64-column slabs of K.  Per slab the producer warp
+// TMA-loads the x tile (64 x 64, 128-byte swizzle) and the matching lora_down
+// slab (64 x R) into one ring stage; the {smooth, 1/smooth} table is read
+// straight from global memory (it is 8 bytes per column and L2-resident).
+// Two consumers read the stage: the MMA warp accumulates x_tile @ lora_down_slab
+// into a [64 x R] fp32 accumulator in tensor memory, and sixteen quantize warps
+// turn the tile into codes and scales.  x is read from HBM exactly once.  With
+// KS = 2 the two partial accumulators are summed in a fixed order through
+// distributed shared memory: no atomics, no zero-fill, no scratch in global
+// memory.  (64-row tiles with pairs, not 128-row tiles with quads: a B200 keeps
+// at most 33 four-CTA clusters of this size resident, one short of the 34 row
+// tiles of a 4352-row activation, while 68 pairs fit in one wave.)
 //
 // Exact arithmetic.  x / smooth must equal the IEEE quotient.  It is computed
-// as q0 = x*r, e = fma(-s, q0, x), q = fma(e, r, q0) with r = RN(1/s) held in
-// shared memory; for operands with at most 11 significant bits this is the
-// correctly rounded quotient (checked exhaustively over mantissas).  Columns
-// whose smooth lies outside [2^-60, 2^60] switch the CTA to __fdiv_rn.
+// as q0 = x*r, e = fma(-s, q0, x), q = fma(e, r, q0) with r = RN(1/s) from the
+// table; for operands with at most 11 significant bits this is the correctly
+// rounded quotient (checked exhaustively over mantissas), provided nothing
+// over- or underflows: the table builder raises a flag when a smooth value lies
+// outside [2^-60, 2^60] and the kernel then divides with __fdiv_rn.  amax / 6
+// uses the same three-step form (checked exhaustively as well).
 #include "nvfp4_math.cuh"
 #include "sm100.cuh"
 #include "svdq_internal.h"
+
 #include <cstdlib>
+#include <type_traits>
 
 namespace svdq {
 namespace qf {
 
-constexpr int TILE_M = 128;
+constexpr int TILE_M = 64;
 constexpr int SLAB_K = 64;                 // columns per ring stage (128 bytes of 16-bit x)
-constexpr int X_BYTES = TILE_M * 128;      // 16 KB
-constexpr int QUANT_WARPS = 8;
+constexpr int X_BYTES = TILE_M * 128;      // 8 KB
+constexpr int QUANT_WARPS = 16;
+constexpr int QUANT_GROUPS = 4;            // groups of 4 warps take slabs round-robin
 constexpr int NUM_THREADS = (2 + QUANT_WARPS) * 32;
-constexpr int MAX_KRANGE = 4096;           // columns per CTA whose (smooth, 1/smooth) fit the table
 
 template <int RP>
 struct Cfg {
   static constexpr int W_BYTES = SLAB_K * RP * 2;                 // lora_down slab
   static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
-  static constexpr int STAGES = RP <= 64 ? 7 : (RP <= 128 ? 6 : 4);
+  static constexpr int STAGES_RAW = (232448 - 1024 - 512) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : (STAGES_RAW / 4) * 4;   // a multiple of the group count
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int TABLE_BYTES = MAX_KRANGE * 8;              // float2 {smooth, 1/smooth}
-  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + TABLE_BYTES + 256;
+  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512;
   static constexpr int TMEM_COLS = RP < 32 ? 32 : RP;             // power of two >= 32
+  static constexpr int EPI_COLS = RP / 4 < 32 ? 32 : RP / 4;      // accumulator columns per epilogue warp
   static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the ring");
+  static_assert(STAGES >= 4 && STAGES % QUANT_GROUPS == 0, "ring depth");
 };
 
 struct Params {
-  const void* smooth;     // [K] or null
+  const float2* table;    // [K] {smooth, 1/smooth} followed by one flag word, or null (no smoothing)
   uint8_t* act;           // [M_pad, K/2]
   uint8_t* scales;        // [K/16, M_pad]
   uint8_t* scales_swz;    // atom order or null
   float* lora;            // [M_pad, R]
-  void* lora16;           // [M_pad, R] or null
+  void* lora16;           // 16-bit form of lora (fp16 [M_pad, R] or bf16 [2, M_pad, R]) or null
   int M, K, R, M_pad;
-  int dbg;   // TEMP diagnostic switches
+  int dbg;                // TEMP diagnostic switches
 };
 
 template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t v);
@@ -67,20 +77,74 @@ template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
 template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
   return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
 }
-template <typename T> __device__ __forceinline__ uint32_t pack2_rn(float a, float b);
-template <> __device__ __forceinline__ uint32_t pack2_rn<__half>(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
-template <> __device__ __forceinline__ uint32_t pack2_rn<__nv_bfloat16>(float a, float b) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
 
 // float4 slot of (row, c4) in the partial-accumulator buffer; the XOR spreads the
-// 32 rows a warp writes at once over all bank groups.
+// rows a warp writes at once over all bank groups.
 __device__ __forceinline__ uint32_t partial_slot(uint32_t row, uint32_t c4, uint32_t rp4) {
   return row * rp4 + (c4 ^ (row & 7u));
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack_group(const uint4& lo16, const uint4& hi16, float (&f)[16]) {
+  const uint32_t w[8] = {lo16.x, lo16.y, lo16.z, lo16.w, hi16.x, hi16.y, hi16.z, hi16.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float2 v = unpack2<T>(w[j]);
+    f[2 * j] = v.x; f[2 * j + 1] = v.y;
+  }
+}
+
+// One 16-element group (already widened to fp32): smoothing divide, amax, scale byte, eight code bytes.
+__device__ __forceinline__ void quantize_group(float (&f)[16], const float4* __restrict__ tb,
+                                               bool has_table, bool use_fdiv, uint32_t& code_lo, uint32_t& code_hi,
+                                               uint32_t& sbyte) {
+  if (has_table) {
+    if (!use_fdiv) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 t = tb[j];          // {s0, r0, s1, r1}
+        const float q0 = f[2 * j] * t.y;
+        f[2 * j] = fmaf(fmaf(-t.x, q0, f[2 * j]), t.y, q0);
+        const float q1 = f[2 * j + 1] * t.w;
+        f[2 * j + 1] = fmaf(fmaf(-t.z, q1, f[2 * j + 1]), t.w, q1);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 t = tb[j];
+        f[2 * j] = __fdiv_rn(f[2 * j], t.x);
+        f[2 * j + 1] = __fdiv_rn(f[2 * j + 1], t.z);
+      }
+    }
+  }
+  float m0 = fmaxf(fabsf(f[0]), fabsf(f[1])), m1 = fmaxf(fabsf(f[2]), fabsf(f[3]));
+  float m2 = fmaxf(fabsf(f[4]), fabsf(f[5])), m3 = fmaxf(fabsf(f[6]), fabsf(f[7]));
+#pragma unroll
+  for (int j = 8; j < 16; j += 4) {
+    m0 = fmaxf(m0, fabsf(f[j])); m1 = fmaxf(m1, fabsf(f[j + 1]));
+    m2 = fmaxf(m2, fabsf(f[j + 2])); m3 = fmaxf(m3, fabsf(f[j + 3]));
+  }
+  const float amax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  // amax / 6, correctly rounded (amax is finite and >= 0; tiny quotients are clamped away below)
+  const float r6 = 0.16666667163372039794921875f;   // RN(1/6)
+  const float s0 = amax * r6;
+  float s = fmaf(fmaf(-6.0f, s0, amax), r6, s0);
+  s = fminf(fmaxf(s, 1e-12f), 448.0f);
+  const uint32_t sb = static_cast<uint32_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3));
+  sbyte = sb;
+  float sf = e4m3_to_f32(static_cast<uint8_t>(sb));
+  // zero scale: every non-zero value saturates, zeros stay zero; 2^-147 * {.25 .. 5} are all
+  // positive and below any normal number
+  sf = (sf == 0.0f) ? __uint_as_float(4u) : sf;
+  GroupBounds gb;
+  gb.p[0] = sf * 0.25f; gb.p[1] = sf * 0.75f; gb.p[2] = sf * 1.25f; gb.p[3] = sf * 1.75f;
+  gb.p[4] = sf * 2.5f;  gb.p[5] = sf * 3.5f;  gb.p[6] = sf * 5.0f;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) lo += e2m1_code(f[j], gb) << (4 * j);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) hi += e2m1_code(f[8 + j], gb) << (4 * j);
+  code_lo = lo; code_hi = hi;
 }
 
 template <typename T, int RP>
@@ -90,217 +154,187 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
 
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  float2* table = reinterpret_cast<float2*>(smem + C::RING_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::RING_BYTES + C::TABLE_BYTES);
+  // 1 KB alignment by pointer arithmetic (not an integer round trip) so that the compiler keeps
+  // the shared address space and emits shared-memory loads and stores
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::RING_BYTES);
   uint64_t* full = bars;                       // [STAGES]  producer -> consumers
   uint64_t* empty = bars + C::STAGES;          // [STAGES]  consumers -> producer
   uint64_t* acc_done = bars + 2 * C::STAGES;   // MMA -> epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  volatile int* slow_div = abort_flag + 1;
   const WaitCtx ctx{abort_flag};
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ks = gridDim.y;               // cluster = (1, KS, 1): blockIdx.y is the rank along K
   const uint32_t krank = blockIdx.y;
   const int m0 = blockIdx.x * TILE_M;
+  const bool has_lora = p.R > 0;
+  const bool has_table = p.table != nullptr;
 
   // slabs owned by this CTA
   const int n_slabs = p.K / SLAB_K;
-  const int base = n_slabs / ks, rem = n_slabs % ks;
+  const int base = n_slabs / static_cast<int>(ks), rem = n_slabs % static_cast<int>(ks);
   const int slab_begin = static_cast<int>(krank) * base + (static_cast<int>(krank) < rem ? static_cast<int>(krank) : rem);
   const int my_slabs = base + (static_cast<int>(krank) < rem ? 1 : 0);
   const int k_begin = slab_begin * SLAB_K;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    *slow_div = 0;
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1 + QUANT_WARPS / 2); }
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1 + QUANT_WARPS / QUANT_GROUPS); }
     mbar_init(acc_done, 1);
     fence_barrier_init();
     tma_prefetch_desc(&tmX);
-    if (p.R > 0) tma_prefetch_desc(&tmW);
+    if (has_lora) tma_prefetch_desc(&tmW);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
   }
-  __syncthreads();   // slow_div initialised before anyone may raise it
-  // {smooth, 1/smooth} of this CTA's columns
-  if (p.smooth != nullptr) {
-    const T* sm = static_cast<const T*>(p.smooth);
-    for (int i = threadIdx.x; i < my_slabs * SLAB_K; i += NUM_THREADS) {
-      const float s = to_f32(sm[k_begin + i]);
-      table[i] = make_float2(s, __frcp_rn(s));
-      const float a = fabsf(s);
-      if (!(a >= 8.6736174e-19f && a <= 1.1529215e18f)) *slow_div = 1;   // outside [2^-60, 2^60] or NaN
-    }
-  }
+  // out-of-range smooth anywhere in K (flag word behind the table) selects the IEEE divide
+  const bool use_fdiv = has_table && reinterpret_cast<const uint32_t*>(p.table + p.K)[0] != 0u;
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_acc = *tmem_slot;
-  const bool use_fdiv = *slow_div != 0;
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
-    if (lane == 0) {
-      for (int i = 0; i < my_slabs; ++i) {
-        const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, i)) break;
-        uint8_t* st = smem + s * C::STAGE_BYTES;
-        const int k0 = k_begin + i * SLAB_K;
-        mbar_arrive_expect_tx(&full[s], p.R > 0 ? C::STAGE_BYTES : X_BYTES);
+    const uint32_t stage_bytes = X_BYTES + (has_lora ? C::W_BYTES : 0);
+    for (int i = 0; i < my_slabs; ++i) {
+      const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
+      if (!mbar_wait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, i)) break;
+      uint8_t* st = smem + s * C::STAGE_BYTES;
+      const int k0 = k_begin + i * SLAB_K;
+      if (elect_one()) {
+        mbar_arrive_expect_tx(&full[s], stage_bytes);
         tma_load_2d(st, &tmX, k0, m0, &full[s]);
-        if (p.R > 0) {
+        if (has_lora) {
 #pragma unroll
           for (int b = 0; b < RP / 64; ++b) tma_load_2d(st + X_BYTES + b * (SLAB_K * 128), &tmW, b * 64, k0, &full[s]);
         }
       }
+      __syncwarp();
     }
-    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      constexpr uint64_t kDescA = smem_desc_base(0, 1024, kSwizzle128B);               // x tile, K-major
-      constexpr uint64_t kDescB = smem_desc_base(SLAB_K * 128, 1024, kSwizzle128B);    // lora_down slab, R-major
-      constexpr uint32_t kIdesc = idesc_f16(kBf16, TILE_M, RP, false, true);
-      bool ok = true;
-      for (int i = 0; i < my_slabs && ok; ++i) {
-        const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
-        if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, i)) { ok = false; break; }
-        tc_fence_after_sync();
-        if (p.R > 0 && !(p.dbg & 64)) {
-          const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
-          const uint32_t b_addr = a_addr + X_BYTES;
+    constexpr uint64_t kDescA = smem_desc_base(0, 1024, kSwizzle128B);               // x tile, K-major
+    constexpr uint64_t kDescB = smem_desc_base(SLAB_K * 128, 1024, kSwizzle128B);    // lora_down slab, R-major
+    constexpr uint32_t kIdesc = idesc_f16(kBf16, kBf16, TILE_M, RP, false, true);
+    bool ok = true;
+    for (int i = 0; i < my_slabs && ok; ++i) {
+      const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
+      if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, i)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
+      const uint32_t b_addr = a_addr + X_BYTES;
+      if (elect_one()) {
+        if (has_lora && !(p.dbg & 64)) {
 #pragma unroll
           for (int j = 0; j < SLAB_K / 16; ++j)
             mma_f16<1>(tmem_acc, smem_desc(kDescA, a_addr + j * 32), smem_desc(kDescB, b_addr + j * 2048), kIdesc,
                        (i | j) != 0 ? 1u : 0u);
         }
-        if (p.R > 0) tc_commit(&empty[s]); else mbar_arrive(&empty[s]);
+        if (has_lora) { if (!(p.dbg & 128)) tc_commit(&empty[s]); if (i == my_slabs - 1) tc_commit(acc_done); }
+        else if (!(p.dbg & 128)) mbar_arrive(&empty[s]);
       }
-      if (ok && p.R > 0) tc_commit(acc_done);
+      __syncwarp();
     }
-    __syncwarp();
   } else {
     // ------------------------------ quantize warps ------------------------------
-    const int qw = warp - 2;                  // 0..7
-    const int half_id = qw >> 2;              // which alternate slab this warp group takes
-    const int row = (qw & 3) * 32 + lane;     // row of the tile
-    const int m = m0 + row;
+    const int qw = warp - 2;                  // 0..15
+    const int grp = qw >> 2;                  // takes slabs grp, grp + 4, ...
+    const int g = qw & 3;                     // 16-column group inside the slab
     const int groups = p.K >> 4;
-    const uint32_t xor7 = static_cast<uint32_t>(row & 7);
-    uint8_t* act_row = p.act + static_cast<size_t>(m) * (p.K >> 1);
-    for (int i = half_id; i < my_slabs; i += 2) {
+    uint8_t* const act_base = p.act + static_cast<size_t>(m0) * (p.K >> 1);
+    for (int i = grp; i < my_slabs; i += QUANT_GROUPS) {
       const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
-      if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, 0x10000 + i)) break;
-      const uint8_t* xrow = smem + s * C::STAGE_BYTES + row * 128;
-      uint4 raw[8];
+      // {smooth, 1/smooth} of this warp's 16 columns: the same address in every lane, read through
+      // the read-only path before the wait so that its latency hides behind the barrier
+      float4 tb[8];
+      if (has_table) {
+        const float4* tsrc = reinterpret_cast<const float4*>(p.table + k_begin + i * SLAB_K + g * 16);
 #pragma unroll
-      for (uint32_t c = 0; c < 8; ++c) raw[c] = *reinterpret_cast<const uint4*>(xrow + ((c ^ xor7) << 4));
-      // the stage is no longer needed by this warp
+        for (int j = 0; j < 8; ++j) tb[j] = __ldg(tsrc + j);
+      }
+      if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, 0x10000 + i)) break;
+      const uint8_t* st = smem + s * C::STAGE_BYTES;
+      uint4 raw[2][2];
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        const uint32_t row = lane + 32 * rr;
+        const uint8_t* xrow = st + row * 128;
+        raw[rr][0] = *reinterpret_cast<const uint4*>(xrow + (((2 * g) ^ (row & 7)) << 4));
+        raw[rr][1] = *reinterpret_cast<const uint4*>(xrow + (((2 * g + 1) ^ (row & 7)) << 4));
+      }
+      float f[2][16];
+      unpack_group<T>(raw[0][0], raw[0][1], f[0]);
+      unpack_group<T>(raw[1][0], raw[1][1], f[1]);
+      // Hand the stage back.  The ring was read through the generic proxy and will be overwritten
+      // through the async proxy (TMA); mbarrier arrivals are performed by a separate unit and do not
+      // wait for earlier shared-memory loads, so without these fences the refill can overtake the reads.
+      __threadfence_block();
+      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
-
       if (p.dbg & 16) continue;
-      const int kl = i * SLAB_K;              // column offset inside this CTA's range
-      uint32_t codes[8];
-      uint32_t sbytes = 0;
+
+      const int k0 = k_begin + i * SLAB_K + g * 16;
+      const int gi = k0 >> 4;
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        float f[16];
-        const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw[2 * g]);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float2 v = unpack2<T>(w[j]);
-          f[2 * j] = v.x; f[2 * j + 1] = v.y;
-        }
-        if (p.smooth != nullptr) {
-          const float4* tb = reinterpret_cast<const float4*>(table + kl + g * 16);
-          if (!use_fdiv) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 t = tb[j];          // {s0, r0, s1, r1}
-              float q0 = f[2 * j] * t.y;
-              float e0 = fmaf(-t.x, q0, f[2 * j]);
-              f[2 * j] = fmaf(e0, t.y, q0);
-              float q1 = f[2 * j + 1] * t.w;
-              float e1 = fmaf(-t.z, q1, f[2 * j + 1]);
-              f[2 * j + 1] = fmaf(e1, t.w, q1);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 t = tb[j];
-              f[2 * j] = __fdiv_rn(f[2 * j], t.x);
-              f[2 * j + 1] = __fdiv_rn(f[2 * j + 1], t.z);
-            }
-          }
-        }
-        float amax = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
-        const uint8_t sb = scale_byte_from_amax(amax);
-        sbytes |= static_cast<uint32_t>(sb) << (8 * g);
-        const GroupBounds gb = bounds_for_scale(e4m3_to_f32(sb));
-        uint32_t lo = 0, hi = 0;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) lo |= e2m1_code(f[j], gb) << (4 * j);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) hi |= e2m1_code(f[8 + j], gb) << (4 * j);
-        codes[2 * g] = lo; codes[2 * g + 1] = hi;
+      for (int rr = 0; rr < 2; ++rr) {
+        const int row = lane + 32 * rr;
+        uint32_t clo, chi, sb;
+        quantize_group(f[rr], tb, has_table, use_fdiv, clo, chi, sb);
+        if ((p.dbg & 32) && clo != 0x12345678u) continue;
+        *reinterpret_cast<uint2*>(act_base + static_cast<size_t>(row) * (p.K >> 1) + (k0 >> 1)) = make_uint2(clo, chi);
+        p.scales[static_cast<size_t>(gi) * p.M_pad + m0 + row] = static_cast<uint8_t>(sb);
+        if (p.scales_swz != nullptr) p.scales_swz[sf_swizzled_offset(m0 + row, gi, groups)] = static_cast<uint8_t>(sb);
       }
-      const int k0 = k_begin + kl;
-      if ((p.dbg & 32) && codes[0] != 0x12345678u) continue;
-      uint4* dst = reinterpret_cast<uint4*>(act_row + (k0 >> 1));
-      dst[0] = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-      dst[1] = make_uint4(codes[4], codes[5], codes[6], codes[7]);
-      const int g0 = k0 >> 4;
-#pragma unroll
-      for (int g = 0; g < 4; ++g) p.scales[static_cast<size_t>(g0 + g) * p.M_pad + m] = static_cast<uint8_t>(sbytes >> (8 * g));
-      if (p.scales_swz != nullptr)
-        *reinterpret_cast<uint32_t*>(p.scales_swz + sf_swizzled_offset(m, g0, groups)) = sbytes;
     }
     // every quantize warp is done reading the ring before it is reused below
     asm volatile("bar.sync 2, %0;" ::"n"(QUANT_WARPS * 32) : "memory");
   }
 
   // ------------------------------ LoRA epilogue ------------------------------
-  if (p.R > 0) {
+  // The 64 accumulator rows live in lanes 0-15 of each 32-lane quarter of tensor memory:
+  // row r is lane (r % 16) + 32 * (r / 16).
+  if (has_lora) {
     constexpr uint32_t RP4 = RP / 4;
     float4* partial = reinterpret_cast<float4*>(smem);       // reuses the ring
     if (warp >= 2) {
       const int qw = warp - 2;
       const int quarter = warp & 3;                           // TMEM lanes this warp may read
-      const int chalf = (qw >> 2);                            // column half
-      const uint32_t row = quarter * 32 + lane;
-      const bool ok = mbar_wait(acc_done, 0, ctx, kDevWaitAcc, 0);
-      tc_fence_after_sync();
-      constexpr int COLS_PER_WARP = RP / 2;
+      const int cpart = qw >> 2;                              // column part
+      if (cpart * C::EPI_COLS < RP) {
+        const bool ok = mbar_wait(acc_done, 0, ctx, kDevWaitAcc, 0);
+        tc_fence_after_sync();
+        const uint32_t row = quarter * 16 + (lane & 15);
 #pragma unroll 1
-      for (int c0 = chalf * COLS_PER_WARP; c0 < (chalf + 1) * COLS_PER_WARP; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
-        tmem_ld_wait();
-        if (ks > 1) {
+        for (int c0 = cpart * C::EPI_COLS; c0 < (cpart + 1) * C::EPI_COLS; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+          tmem_ld_wait();
+          if (lane < 16) {
+            if (ks > 1) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            partial[partial_slot(row, (c0 >> 2) + j, RP4)] =
-                make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-        } else if (ok) {
-          const size_t gm = static_cast<size_t>(m0 + row);
+              for (int j = 0; j < 8; ++j)
+                partial[partial_slot(row, (c0 >> 2) + j, RP4)] =
+                    make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+            } else if (ok) {
+              const size_t gm = static_cast<size_t>(m0 + row);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int c = c0 + 4 * j;
-            if (c < p.R) {
-              *reinterpret_cast<float4*>(p.lora + gm * p.R + c) =
-                  make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-              if (p.lora16 != nullptr)
-                *reinterpret_cast<uint2*>(static_cast<T*>(p.lora16) + gm * p.R + c) =
-                    make_uint2(pack2_rn<T>(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1])),
-                               pack2_rn<T>(__uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+              for (int j = 0; j < 8; ++j) {
+                const int c = c0 + 4 * j;
+                if (c < p.R) {
+                  *reinterpret_cast<float4*>(p.lora + gm * p.R + c) =
+                      make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                  if (p.lora16 != nullptr)
+                    store_lora16x4<T>(p.lora16, gm * p.R + c, static_cast<size_t>(p.M_pad) * p.R,
+                                      make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                  __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+                }
+              }
             }
           }
         }
@@ -308,8 +342,9 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     }
     if (ks > 1) {
       tc_fence_before_sync();
+      __syncwarp();
       cluster_sync_all();                                     // every CTA's partial is in its shared memory
-      // CTA k sums rows [k*128/KS, (k+1)*128/KS) over the cluster, in rank order
+      // CTA k sums rows [k*64/KS, (k+1)*64/KS) over the cluster, in rank order
       const uint32_t rows_per = TILE_M / ks;
       const uint32_t row_lo = krank * rows_per;
       const uint32_t items = rows_per * RP4;
@@ -326,9 +361,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         if (c < p.R) {
           const size_t gm = static_cast<size_t>(m0 + row);
           *reinterpret_cast<float4*>(p.lora + gm * p.R + c) = acc;
-          if (p.lora16 != nullptr)
-            *reinterpret_cast<uint2*>(static_cast<T*>(p.lora16) + gm * p.R + c) =
-                make_uint2(pack2_rn<T>(acc.x, acc.y), pack2_rn<T>(acc.z, acc.w));
+          if (p.lora16 != nullptr) store_lora16x4<T>(p.lora16, gm * p.R + c, static_cast<size_t>(p.M_pad) * p.R, acc);
         }
       }
       cluster_sync_all();                                     // nobody leaves while its memory is being read
@@ -348,6 +381,23 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   }
 }
 
+// {smooth, 1/smooth} per column, then one flag word: 1 if any |smooth| lies outside
+// [2^-60, 2^60] (or is NaN), where the three-step divide could over- or underflow.
+template <typename T>
+__global__ void smooth_table_kernel(const T* __restrict__ smooth, float2* __restrict__ table, int K) {
+  __shared__ int bad;
+  if (threadIdx.x == 0) bad = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < K; i += blockDim.x) {
+    const float s = to_f32(smooth[i]);
+    table[i] = make_float2(s, __frcp_rn(s));
+    const float a = fabsf(s);
+    if (!(a >= 8.6736174e-19f && a <= 1.1529215e18f)) bad = 1;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *reinterpret_cast<uint2*>(table + K) = make_uint2(bad ? 1u : 0u, 0u);
+}
+
 }  // namespace qf
 
 // How many CTAs share one row tile along K (0 = no admissible split).
@@ -357,9 +407,8 @@ static int pick_k_split(int M_pad, int K) {
   const int sms = sm_count();
   int best = 0;
   double best_cost = 1e30;
-  for (int ks : {1, 2, 4}) {
+  for (int ks : {1, 2}) {
     if (ks > slabs) continue;
-    if (((slabs + ks - 1) / ks) * qf::SLAB_K > qf::MAX_KRANGE) continue;
     const int ctas = tiles * ks;
     const int waves = (ctas + sms - 1) / sms;
     const double cost = static_cast<double>(waves) * ((slabs + ks - 1) / ks) + 2.0 * (ks > 1);
@@ -373,6 +422,16 @@ bool quantize_fused_supported(int M, int K, int R, int M_pad) {
   if (M_pad % qf::TILE_M != 0 || K % qf::SLAB_K != 0) return false;
   if (R < 0 || R > 256 || R % 8 != 0) return false;
   return pick_k_split(M_pad, K) != 0;
+}
+
+int launch_smooth_table(const void* smooth, void* table, int K, int dtype, cudaStream_t stream) {
+  if (dtype == SVDQ_DTYPE_F16)
+    qf::smooth_table_kernel<__half><<<1, 1024, 0, stream>>>(static_cast<const __half*>(smooth), static_cast<float2*>(table), K);
+  else if (dtype == SVDQ_DTYPE_BF16)
+    qf::smooth_table_kernel<__nv_bfloat16><<<1, 1024, 0, stream>>>(static_cast<const __nv_bfloat16*>(smooth), static_cast<float2*>(table), K);
+  else
+    return SVDQ_ERR_DTYPE;
+  return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;
 }
 
 template <typename T, int RP>
@@ -434,12 +493,12 @@ int quantize_fused_max_clusters(int R, int ks, int dtype) {
   return rp == 64 ? max_clusters_t<__nv_bfloat16, 64>(ks) : rp == 128 ? max_clusters_t<__nv_bfloat16, 128>(ks) : max_clusters_t<__nv_bfloat16, 256>(ks);
 }
 
-int launch_quantize_fused(const void* x, const void* lora_down, const void* smooth, void* act, void* ascales,
+int launch_quantize_fused(const void* x, const void* lora_down, const void* smooth_table, void* act, void* ascales,
                           float* lora_act, void* ascales_swz, void* lora_act16, int M, int K, int R, int M_pad,
                           int dtype, cudaStream_t stream) {
   if (!quantize_fused_supported(M, K, R, M_pad)) return SVDQ_ERR_UNSUPPORTED;
   qf::Params p;
-  p.smooth = smooth;
+  p.table = static_cast<const float2*>(smooth_table);
   p.act = static_cast<uint8_t*>(act);
   p.scales = static_cast<uint8_t*>(ascales);
   p.scales_swz = static_cast<uint8_t*>(ascales_swz);

@@ -82,7 +82,7 @@ quantize_rows_kernel(const T* __restrict__ x, const T* __restrict__ smooth, uint
 // 8 rows per block; threads stride over r so the w reads are coalesced.
 template <typename T>
 __global__ void __launch_bounds__(128)
-lora_down_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restrict__ out, T* __restrict__ out16,
+lora_down_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __restrict__ out, void* __restrict__ out16,
                  int M, int M_pad, int K, int R) {
   constexpr int ROWS = 8, KC = 128;
   __shared__ float xs[ROWS][KC];
@@ -115,7 +115,7 @@ lora_down_kernel(const T* __restrict__ x, const T* __restrict__ w, float* __rest
         const int m = m0 + i;
         if (m < M_pad) {
           out[static_cast<size_t>(m) * R + r] = acc[i];
-          if (out16 != nullptr) out16[static_cast<size_t>(m) * R + r] = static_cast<T>(acc[i]);
+          if (out16 != nullptr) store_lora16<T>(out16, static_cast<size_t>(m) * R + r, static_cast<size_t>(M_pad) * R, acc[i]);
         }
       }
     }
@@ -132,11 +132,12 @@ __global__ void swizzle_scales_kernel(const uint8_t* __restrict__ src, uint8_t* 
   }
 }
 
+// fp32 lora_act -> the 16-bit form of type T (see store_lora16)
 template <typename T>
-__global__ void cast_f32_kernel(const float* __restrict__ src, T* __restrict__ dst, long long n) {
+__global__ void cast_lora16_kernel(const float* __restrict__ src, void* __restrict__ dst, long long n) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x)
-    dst[i] = static_cast<T>(src[i]);
+    store_lora16<T>(dst, static_cast<size_t>(i), static_cast<size_t>(n), src[i]);
 }
 
 static int grid_for(long long items, int block) {
@@ -174,9 +175,9 @@ int launch_lora_down(const void* x, const void* w, float* out, void* out16, int 
   if (M_pad == 0 || R == 0) return SVDQ_OK;
   const int grid = (M_pad + 7) / 8;
   if (dtype == SVDQ_DTYPE_F16)
-    lora_down_kernel<__half><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), static_cast<const __half*>(w), out, static_cast<__half*>(out16), M, M_pad, K, R);
+    lora_down_kernel<__half><<<grid, 128, 0, stream>>>(static_cast<const __half*>(x), static_cast<const __half*>(w), out, out16, M, M_pad, K, R);
   else if (dtype == SVDQ_DTYPE_BF16)
-    lora_down_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), out, static_cast<__nv_bfloat16*>(out16), M, M_pad, K, R);
+    lora_down_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), out, out16, M, M_pad, K, R);
   else
     return SVDQ_ERR_DTYPE;
   return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;
@@ -192,9 +193,9 @@ int launch_swizzle_scales(const void* src, void* dst, int groups, int rows, cuda
 int launch_cast_f32(const float* src, void* dst, long long n, int dtype, cudaStream_t stream) {
   if (n == 0) return SVDQ_OK;
   if (dtype == SVDQ_DTYPE_F16)
-    cast_f32_kernel<__half><<<grid_for(n, 256), 256, 0, stream>>>(src, static_cast<__half*>(dst), n);
+    cast_lora16_kernel<__half><<<grid_for(n, 256), 256, 0, stream>>>(src, dst, n);
   else if (dtype == SVDQ_DTYPE_BF16)
-    cast_f32_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, stream>>>(src, static_cast<__nv_bfloat16*>(dst), n);
+    cast_lora16_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, stream>>>(src, dst, n);
   else
     return SVDQ_ERR_DTYPE;
   return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;

@@ -154,6 +154,23 @@ __device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorM
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
+// Tiled load whose completion bytes are counted on the barrier at the shared::cluster address
+// `bar`.  CG = 1: a barrier of this CTA.  CG = 2: the .cta_group::2 form, which lets either CTA
+// of a pair count its bytes on the partner's barrier.
+template <int CG>
+__device__ __forceinline__ void tma_load_2d_bar(void* smem_dst, const CUtensorMap* m, int x, int y, uint32_t bar) {
+  if constexpr (CG == 1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+  }
+}
 // 1-D bulk load (both addresses 16-byte aligned, size a multiple of 16)
 __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
   asm volatile(
@@ -244,8 +261,9 @@ constexpr uint32_t kSwizzleNone = 0, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle
 // Instruction descriptor, dense 16-bit kinds (upper 32 bits of the "idesc" operand):
 //   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
 //   [15] A major (0 = K)  [16] B major (0 = K, 1 = MN)  [17,23) N >> 3  [24,29) M >> 4
-__host__ __device__ constexpr uint32_t idesc_f16(bool bf16, uint32_t M, uint32_t N, bool a_mn_major, bool b_mn_major) {
-  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+// A and B formats are independent: an fp16 A can meet a bf16 B.
+__host__ __device__ constexpr uint32_t idesc_f16(bool a_bf16, bool b_bf16, uint32_t M, uint32_t N, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
          ((b_mn_major ? 1u : 0u) << 16) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 // Block-scaled FP4 kind (mxf4nvf4): A/B format 1 = E2M1, scale format 0 = UE4M3,
@@ -311,6 +329,20 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
 __device__ __forceinline__ void tc_commit_pair(uint64_t* bar, uint16_t cta_mask) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                ::"r"(smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+
+// Pair form that arrives only on the issuing CTA's barrier (tracks the pair's prior tcgen05 ops).
+__device__ __forceinline__ void tc_commit_pair_local(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(smem_u32(bar)) : "memory");
+}
+template <int CG>
+__device__ __forceinline__ void tc_commit_local(uint64_t* bar) {
+  if constexpr (CG == 1) tc_commit(bar); else tc_commit_pair_local(bar);
+}
+template <int CG>
+__device__ __forceinline__ void tc_commit_mask(uint64_t* bar, uint16_t cta_mask) {
+  if constexpr (CG == 1) tc_commit(bar); else tc_commit_pair(bar, cta_mask);
 }
 
 // ---------------------------------------------------------------------------

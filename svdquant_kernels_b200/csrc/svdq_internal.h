@@ -19,7 +19,8 @@ int launch_cast_f32(const float* src, void* dst, long long n, int dtype, cudaStr
 
 // quantize_fused.cu
 bool quantize_fused_supported(int M, int K, int R, int M_pad);
-int launch_quantize_fused(const void* x, const void* lora_down, const void* smooth, void* act, void* ascales,
+int launch_smooth_table(const void* smooth, void* table, int K, int dtype, cudaStream_t stream);
+int launch_quantize_fused(const void* x, const void* lora_down, const void* smooth_table, void* act, void* ascales,
                           float* lora_act, void* ascales_swz, void* lora_act16, int M, int K, int R, int M_pad,
                           int dtype, cudaStream_t stream);
 

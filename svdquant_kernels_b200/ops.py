@@ -18,7 +18,10 @@ Two layout seams are hidden here.  The tensor core reads block scales in a
 128-row x 4-group atom order and reads the LoRA activations as 16-bit values,
 while the API tensors are the reference's canonical `[K/16, rows]` scales and an
 fp32 `lora_act`.  The quantizer therefore also writes both twins and attaches
-them to the tensors it returns; `gemm_w4a4` picks them up when the tensors
+them to the tensors it returns (the 16-bit twin is one fp16 plane, or for bf16 a
+hi plane and a lo plane whose sum carries 16 significant bits, because the dense
+MMA needs lora_act in lora_up's format and a single bf16 copy is too coarse);
+`gemm_w4a4` picks them up when the tensors
 arrive unmodified, and otherwise (tensors from elsewhere, e.g. weight scales)
 derives them once with two small kernels of the same library and caches them
 on the tensor object.
@@ -57,6 +60,21 @@ def _attached(owner: torch.Tensor) -> Optional[torch.Tensor]:
     return twin
 
 
+def _smooth_table(smooth: torch.Tensor) -> torch.Tensor:
+    """{smooth, 1/smooth} pairs + flag word for the fused kernel; built once per smooth tensor."""
+    twin = _attached(smooth)
+    if twin is not None:
+        return twin
+    K = smooth.shape[0]
+    lib = _lib.load()
+    table = torch.empty(2 * K + 4, dtype=torch.float32, device=smooth.device)
+    with torch.cuda.device(smooth.device):
+        rc = lib.svdq_prepare_smooth(_ptr(smooth), _ptr(table), K, _DT[smooth.dtype], _stream(smooth.device))
+    _lib.check(rc, "prepare_smooth")
+    _attach(smooth, table)
+    return table
+
+
 def quantize_w4a4_act_fuse_lora(
     input: torch.Tensor,
     lora_down: torch.Tensor,
@@ -90,15 +108,22 @@ def quantize_w4a4_act_fuse_lora(
     x = input.contiguous()
     ld = lora_down.contiguous()
     sm = None if smooth is None else smooth.contiguous()
+    table = None
+    if sm is not None and _force != _lib.QUANT_FORCE_GENERIC:
+        table = _smooth_table(sm)
     act = torch.empty((M_pad, K // 2), dtype=torch.uint8, device=dev)
     ascales = torch.empty((K // 16, M_pad), dtype=torch.float8_e4m3fn, device=dev)
     lora_act = torch.empty((M_pad, R), dtype=torch.float32, device=dev)
     want_swz = M_pad % 128 == 0 and K % 64 == 0 and M_pad > 0
     swz = torch.empty(M_pad * (K // 16), dtype=torch.uint8, device=dev) if want_swz else None
-    la16 = torch.empty((M_pad, R), dtype=input.dtype, device=dev) if R > 0 else None
+    # 16-bit form of lora_act for the GEMM: one fp16 plane, or bf16 hi and lo planes
+    la16 = None
+    if R > 0:
+        shape16 = (M_pad, R) if input.dtype == torch.float16 else (2, M_pad, R)
+        la16 = torch.empty(shape16, dtype=input.dtype, device=dev)
     with torch.cuda.device(dev):
         rc = lib.svdq_quantize_w4a4_act_fuse_lora(
-            _ptr(x), _ptr(ld), _ptr(sm), _ptr(act), _ptr(ascales), _ptr(lora_act), _ptr(swz), _ptr(la16),
+            _ptr(x), _ptr(ld), _ptr(sm), _ptr(table), _ptr(act), _ptr(ascales), _ptr(lora_act), _ptr(swz), _ptr(la16),
             M, K, R, M_pad, _DT[input.dtype], _force, _stream(dev))
     _lib.check(rc, "quantize_w4a4_act_fuse_lora")
     if swz is not None:
@@ -150,15 +175,17 @@ def swizzle_scales(scales: torch.Tensor) -> torch.Tensor:
 
 
 def _lora_act_16(lora_act_in: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    if lora_act_in.dtype == out_dtype:
-        return lora_act_in.contiguous()
+    """lora_act in the 16-bit form the GEMM consumes: fp16 `[M, R]`, or bf16 hi/lo planes `[2, M, R]`."""
     twin = _attached(lora_act_in)
     if twin is not None and twin.dtype == out_dtype:
         return twin
-    assert lora_act_in.dtype == torch.float32, "lora_act_in must be fp32 or already out_dtype"
+    if lora_act_in.dtype == torch.float16 and out_dtype == torch.float16:
+        return lora_act_in.contiguous()
+    src = lora_act_in if lora_act_in.dtype == torch.float32 else lora_act_in.float()
     lib = _lib.load()
-    src = lora_act_in.contiguous()
-    out = torch.empty(src.shape, dtype=out_dtype, device=src.device)
+    src = src.contiguous()
+    shape16 = tuple(src.shape) if out_dtype == torch.float16 else (2,) + tuple(src.shape)
+    out = torch.empty(shape16, dtype=out_dtype, device=src.device)
     with torch.cuda.device(src.device):
         rc = lib.svdq_cast_lora_act(_ptr(src), _ptr(out), src.numel(), _DT[out_dtype], _stream(src.device))
     _lib.check(rc, "cast_lora_act")
@@ -215,8 +242,9 @@ def gemm_w4a4(
     assert K % 64 == 0, f"K ({K}) must be a multiple of 64 for NVFP4 scale atoms"
     variant = 0
     if tiler_mn is not None:
-        assert tiler_mn[1] in (128, 256) and N % tiler_mn[1] == 0
-        variant = tiler_mn[1]
+        assert tiler_mn[0] in (128, 256) and tiler_mn[1] in (128, 256)
+        assert M % tiler_mn[0] == 0 and N % tiler_mn[1] == 0
+        variant = (2000 if tiler_mn[0] == 256 else 0) + tiler_mn[1]
 
     lib = _lib.load()
     dev = act.device

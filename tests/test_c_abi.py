@@ -40,15 +40,15 @@ def test_argument_validation_needs_no_device(lib_path):
     p = ctypes.addressof(buf)
     p = (p + 15) & ~15
     # K not a multiple of 16
-    assert lib.svdq_quantize_w4a4_act_fuse_lora(p, p, None, p, p, p, None, None, 4, 24, 0, 4, 0, 0, None) == 2
+    assert lib.svdq_quantize_w4a4_act_fuse_lora(p, p, None, None, p, p, p, None, None, 4, 24, 0, 4, 0, 0, None) == 2
     # unsupported dtype
-    assert lib.svdq_quantize_w4a4_act_fuse_lora(p, p, None, p, p, p, None, None, 4, 32, 0, 4, 2, 0, None) == 3
+    assert lib.svdq_quantize_w4a4_act_fuse_lora(p, p, None, None, p, p, p, None, None, 4, 32, 0, 4, 2, 0, None) == 3
     # missing output
-    assert lib.svdq_quantize_w4a4_act_fuse_lora(p, p, None, None, p, p, None, None, 4, 32, 0, 4, 0, 0, None) == 1
+    assert lib.svdq_quantize_w4a4_act_fuse_lora(p, p, None, None, None, p, p, None, None, 4, 32, 0, 4, 0, 0, None) == 1
     # misaligned input
-    assert lib.svdq_quantize_w4a4_act_fuse_lora(p + 2, p, None, p, p, p, None, None, 4, 32, 0, 4, 0, 0, None) == 4
+    assert lib.svdq_quantize_w4a4_act_fuse_lora(p + 2, p, None, None, p, p, p, None, None, 4, 32, 0, 4, 0, 0, None) == 4
     # empty problem is a no-op
-    assert lib.svdq_quantize_w4a4_act_fuse_lora(None, None, None, None, None, None, None, None, 0, 32, 0, 0, 0, 0, None) == 0
+    assert lib.svdq_quantize_w4a4_act_fuse_lora(None, None, None, None, None, None, None, None, None, 0, 32, 0, 0, 0, 0, None) == 0
     # GEMM contract
     assert lib.svdq_gemm_w4a4_supported(256, 128, 128, 16) == 1
     assert lib.svdq_gemm_w4a4_supported(4352, 15360, 3840, 128) == 1

@@ -85,9 +85,11 @@ def test_affine_switches(wc, bias):
     assert _case(256, 512, 256, 32, torch.float16, seed=1, wc=wc, bias=bias) <= TOL
 
 
-@pytest.mark.parametrize("tiler", [(128, 128), (128, 256)])
-def test_both_n_tiles(tiler):
-    assert _case(384, 768, 512, 64, torch.bfloat16, seed=2, tiler=tiler) <= TOL
+@pytest.mark.parametrize("tiler", [(128, 128), (128, 256), (256, 128), (256, 256)])
+def test_every_tile_shape(tiler):
+    """One CTA per 128-row tile and CTA pairs on 256-row tiles, both N tile widths."""
+    assert _case(512, 768, 512, 64, torch.bfloat16, seed=2, tiler=tiler) <= TOL
+    assert _case(256, 320, 256, 16, torch.float16, seed=3, tiler=tiler) <= TOL
 
 
 def test_main_product_is_exact_without_lora():
@@ -121,11 +123,11 @@ def test_linearity_property_full_size():
     y1 = ops.gemm_w4a4(act, wgt, asc, wsc, la, lu, None, None, dt).float()
     torch.cuda.synchronize()
     assert_device_clean()
-    want = la.to(dt).float() @ lu.float().T
+    want = la @ lu.float().T
     diff = (y1 - y0)
-    # both y are bf16-rounded, so compare against the size of y itself
+    # both y are bf16-rounded (2^-9 relative each), so compare against the size of y itself
     err = (diff - want).norm() / y1.norm()
-    assert err.item() <= 6e-3
+    assert err.item() <= 4e-3
     # and the main product alone against a dequantised fp32 matmul on a slab of rows
     a = torch.from_numpy(O.dequantize_nvfp4_rows(u8(act[:256]), u8(asc[:, :256]))).cuda()
     wd = torch.from_numpy(O.dequantize_nvfp4_rows(u8(wgt), u8(wsc))).cuda()
