@@ -9,16 +9,17 @@
 // The reference's own kernel for this op is
 // cute_kernels/gemm_w4a4/kernel_v2_fa4.py:841-1589.
 //
-// Work decomposition (352 threads per CTA, one CTA per SM):
+// Work decomposition (384 threads per CTA, one CTA per SM):
 //   warps 0-7  epilogue: tensor memory -> registers -> affine -> 16 bit ->
 //              swizzled shared memory -> TMA store (a 32-row x BN/2 strip per warp)
 //   warp  8    producer: TMA loads into a ring of shared-memory stages
 //   warp  9    MMA issuer: tcgen05.mma + commits
-//   warp  10   scale copier: tcgen05.cp of the stage's scale atoms into a
-//              double-buffered scale area of tensor memory, one slab ahead
+//   warps 10-11 scale copiers: tcgen05.cp of the stage's scale atoms into a
+//              multi-buffered scale area of tensor memory, a few slabs ahead;
+//              each warp takes two of the slab's four k-blocks
 // Issuing one tcgen05 instruction costs tens of cycles of a single thread, and a
 // 256-wide slab needs 12 scale copies next to its 4 MMAs, so the two kinds are
-// issued by different warps and handshake through mbarriers.  All three
+// issued by different warps and handshake through mbarriers.  All
 // single-lane roles stay converged and elect one lane per instruction, so
 // descriptors and addresses live in uniform registers.
 //
@@ -58,7 +59,8 @@ constexpr int BK = 256;          // K elements per stage (128 bytes of codes per
 constexpr int A_BYTES = BM * 128;
 constexpr int SFA_BYTES = BM * (BK / 16);  // 2048
 constexpr int EPI_WARPS = 8;
-constexpr int NUM_THREADS = (EPI_WARPS + 3) * 32;
+constexpr int SF_WARPS = 2;       // scale copiers: each takes two of a slab's four k-blocks
+constexpr int NUM_THREADS = (EPI_WARPS + 2 + SF_WARPS) * 32;
 constexpr int STORE_BUF_BYTES = 32 * 128;  // one 32-row x 64-column strip of y
 
 template <int CG, int BN>
@@ -79,12 +81,16 @@ struct Cfg {
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SFA_COLS = 16;                 // 4 k-blocks x 4 columns
   static constexpr int SFB_COLS = 4 * (BN / 32);      // 4 k-blocks x BN/32 columns
-  static constexpr int SF_COLS = SFA_COLS + SFB_COLS; // one scale buffer; two are kept
+  static constexpr int SF_COLS = SFA_COLS + SFB_COLS; // one scale buffer
+  // Scale buffers in tensor memory.  Copies and MMAs execute in issue order on one pipe, and an MMA
+  // may only be issued once its scales have landed, so the copier has to run several slabs ahead of
+  // the MMA issuer or every slab pays a copy + wake-up bubble.
+  static constexpr int SF_BUFS = (ACC_STAGES * BN + 4 * SF_COLS <= 512) ? 4 : 2;
   static constexpr int TMEM_COLS = 512;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STORE_BYTES + TAIL_BYTES;
-  static_assert(ACC_STAGES * BN + 2 * SF_COLS <= TMEM_COLS, "tensor memory budget");
+  static_assert(ACC_STAGES * BN + SF_BUFS * SF_COLS <= TMEM_COLS, "tensor memory budget");
   static_assert(STAGES >= 3, "ring too shallow");
-  static_assert((2 * STAGES + 2 * ACC_STAGES + 4) * 8 + 16 <= 256, "barrier block");
+  static_assert((2 * STAGES + 2 * ACC_STAGES + 2 * SF_BUFS) * 8 + 16 <= 256, "barrier block");
 };
 
 struct Params {
@@ -140,9 +146,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* empty = bars + C::STAGES;                             // [STAGES]     stage consumed by the MMAs (per CTA)
   uint64_t* acc_full = bars + 2 * C::STAGES;                      // [ACC_STAGES] accumulator complete (per CTA)
   uint64_t* acc_empty = acc_full + C::ACC_STAGES;                 // [ACC_STAGES] accumulator drained (leader's copy is used)
-  uint64_t* sf_full = acc_empty + C::ACC_STAGES;                  // [2] scale buffer copied (leader CTA)
-  uint64_t* sf_empty = sf_full + 2;                               // [2] scale buffer consumed by the MMAs (leader CTA)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + 2);
+  uint64_t* sf_full = acc_empty + C::ACC_STAGES;                  // [SF_BUFS] scale buffer copied (leader CTA)
+  uint64_t* sf_empty = sf_full + C::SF_BUFS;                      // [SF_BUFS] scale buffer consumed by the MMAs (leader CTA)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + C::SF_BUFS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx ctx{abort_flag};
 
@@ -156,7 +162,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     *abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < C::ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EPI_WARPS * CG); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&sf_full[b], 1); mbar_init(&sf_empty[b], 1); }
+    for (int b = 0; b < C::SF_BUFS; ++b) { mbar_init(&sf_full[b], SF_WARPS); mbar_init(&sf_empty[b], 1); }
     fence_barrier_init();
   }
   if (warp == EPI_WARPS && lane == 0) {
@@ -173,7 +179,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if constexpr (CG == 2) cluster_sync_all();   // both CTAs' barriers exist before anything remote touches them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_sf = tmem_base + C::ACC_STAGES * BN;       // two buffers of [SFA 16 | SFB] columns
+  const uint32_t tmem_sf = tmem_base + C::ACC_STAGES * BN;       // SF_BUFS buffers of [SFA 16 | SFB] columns
 
   const int kt_main = (p.K + BK - 1) / BK;   // the last slab may hold fewer than four 64-element k-blocks
   constexpr int kLoraParts = kBf16 ? 2 : 1;        // bf16: hi and lo halves of lora_act
@@ -245,9 +251,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
           if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, it)) { ok = false; break; }
           const bool main_slab = kt < kt_main;
-          const uint32_t sb = sf_it & 1;
+          const uint32_t sb = sf_it % C::SF_BUFS;
           if (main_slab && !(p.dbg & 4)) {
-            if (!mbar_wait(&sf_full[sb], (sf_it >> 1) & 1, ctx, kDevWaitMisc, it)) { ok = false; break; }
+            if (!mbar_wait(&sf_full[sb], (sf_it / C::SF_BUFS) & 1, ctx, kDevWaitMisc, it)) { ok = false; break; }
           }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
@@ -278,20 +284,24 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
     }
-  } else if (warp == EPI_WARPS + 2) {
-    // ------------------------------ scale copier (leader CTA only) ------------------------------
-    // Copies the scale atoms of main slab n into scale buffer n % 2 while the MMAs of slab n - 1 run.
+  } else if (warp >= EPI_WARPS + 2) {
+    // ------------------------------ scale copiers (leader CTA only) ------------------------------
+    // Copies the scale atoms of main slab n into scale buffer n % SF_BUFS, up to SF_BUFS - 1 slabs ahead of the MMAs.
     if (rank == 0 && !(p.dbg & 4)) {
       constexpr uint64_t kDescSF = smem_desc_base(0, 128, kSwizzleNone);    // 8 x 16 B core matrices, 128 B apart
+      const int jlo = (warp - (EPI_WARPS + 2)) * (4 / SF_WARPS);            // this warp's k-blocks: jlo, jlo + 1
       uint32_t it = 0, sf_it = 0;
       bool ok = true;
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
         for (int kt = 0; kt < kt_all; ++kt, ++it) {
-          if (kt >= kt_main) continue;                      // LoRA slabs carry no scales
+          // Every slab's barrier is waited on in order, LoRA slabs (which carry no scales) included: a
+          // waiter that skipped ahead could get two ring revolutions in front of the producer, where the
+          // parity of a barrier no longer tells the revolutions apart.
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
-          const uint32_t sb = sf_it & 1;
-          if (!mbar_wait(&sf_empty[sb], ((sf_it >> 1) & 1) ^ 1, ctx, kDevWaitMisc, 0x20000 + it)) { ok = false; break; }
           if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, 0x20000 + it)) { ok = false; break; }
+          if (kt >= kt_main) continue;
+          const uint32_t sb = sf_it % C::SF_BUFS;
+          if (!mbar_wait(&sf_empty[sb], ((sf_it / C::SF_BUFS) & 1) ^ 1, ctx, kDevWaitMisc, 0x20000 + it)) { ok = false; break; }
           tc_fence_after_sync();
           const uint32_t sfa_addr = smem_u32(smem + s * C::STAGE_BYTES) + A_BYTES + C::B_BYTES;
           const uint32_t sfb_addr = sfa_addr + SFA_BYTES;
@@ -299,7 +309,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const int nkb = min(4, k_groups4 - kt * 4);
           if (elect_one()) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int jj = 0; jj < 4 / SF_WARPS; ++jj) {
+              const int j = jlo + jj;
               if (j < nkb && !((p.dbg & 2) && kt > 0)) {
                 tmem_cp_scales<CG>(tsfa + j * 4, smem_desc(kDescSF, sfa_addr + j * 512));
 #pragma unroll
@@ -337,24 +348,26 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait(&acc_full[as], aph, ctx, kDevWaitAcc, tcount)) ok = false;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN + chalf * (BN / 2);
-#pragma unroll 1
+      // Drain: every column this warp owns goes to registers in one burst, the accumulator is handed
+      // back at once, and only then do the affine, the packing and the stores happen.
+      uint32_t v[C::GROUPS_PER_WARP][2][32];
+#pragma unroll
+      for (int g = 0; g < C::GROUPS_PER_WARP; ++g) {
+        tmem_ld_32x32(taddr + g * 64, v[g][0]);
+        tmem_ld_32x32(taddr + g * 64 + 32, v[g][1]);
+      }
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CG == 2) mbar_arrive_cluster(&acc_empty[as], 0); else mbar_arrive(&acc_empty[as]);
+      }
+#pragma unroll
       for (int g = 0; g < C::GROUPS_PER_WARP; ++g, ++nstore) {
         uint8_t* buf = my_bufs + (nstore % C::STORE_BUFS) * STORE_BUF_BYTES;
         // the TMA store that last read this buffer must be done with it
         if (lane == 0) tma_store_wait_read<C::STORE_BUFS - 1>();
         __syncwarp();
-        uint32_t v[2][32];
-        tmem_ld_32x32(taddr + g * 64, v[0]);
-        tmem_ld_32x32(taddr + g * 64 + 32, v[1]);
-        tmem_ld_wait();
-        if (g == C::GROUPS_PER_WARP - 1) {
-          // every column this warp owns has left tensor memory
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) {
-            if constexpr (CG == 2) mbar_arrive_cluster(&acc_empty[as], 0); else mbar_arrive(&acc_empty[as]);
-          }
-        }
         const int cbase = chalf * (BN / 2) + g * 64;
 #pragma unroll
         for (int hc = 0; hc < 2; ++hc) {
@@ -363,8 +376,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint32_t o[16];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            float a0 = __uint_as_float(v[hc][4 * i]), a1 = __uint_as_float(v[hc][4 * i + 1]);
-            float a2 = __uint_as_float(v[hc][4 * i + 2]), a3 = __uint_as_float(v[hc][4 * i + 3]);
+            float a0 = __uint_as_float(v[g][hc][4 * i]), a1 = __uint_as_float(v[g][hc][4 * i + 1]);
+            float a2 = __uint_as_float(v[g][hc][4 * i + 2]), a3 = __uint_as_float(v[g][hc][4 * i + 3]);
             if (wc != nullptr) {
               const float4 w4 = wc4[i];
               a0 = __fmul_rn(a0, w4.x); a1 = __fmul_rn(a1, w4.y); a2 = __fmul_rn(a2, w4.z); a3 = __fmul_rn(a3, w4.w);
