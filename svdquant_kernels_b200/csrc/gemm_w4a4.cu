@@ -70,11 +70,11 @@ struct Cfg {
   static constexpr int SFB_BYTES = BN * (BK / 16);
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int ACC_STAGES = (BN <= 128) ? 2 : 1;
-  // Staging strips per epilogue warp.  With a whole tile of strips the accumulator is drained at
-  // register speed and released while the TMA stores are still in flight; a single CTA with a
-  // 256-wide tile cannot afford that next to three 54 KB ring stages and keeps two.
+  // One 32-row x 64-column staging strip per epilogue warp.  The accumulator is drained into
+  // registers in one burst and released before any staging happens, so a second strip would only
+  // take shared memory away from the load ring.
   static constexpr int GROUPS_PER_WARP = BN / 128;                 // 64-column strips each epilogue warp handles per tile
-  static constexpr int STORE_BUFS = (CG == 1 && BN == 256) ? 1 : GROUPS_PER_WARP;
+  static constexpr int STORE_BUFS = 1;
   static constexpr int STORE_BYTES = EPI_WARPS * STORE_BUFS * STORE_BUF_BYTES;
   static constexpr int TAIL_BYTES = 2048 /*affine*/ + 256 /*barriers*/;
   static constexpr int STAGES_RAW = (232448 - 1024 - STORE_BYTES - TAIL_BYTES) / STAGE_BYTES;

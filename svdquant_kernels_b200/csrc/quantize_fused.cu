@@ -44,15 +44,17 @@ constexpr int X_BYTES = TILE_M * 128;      // 8 KB
 constexpr int QUANT_WARPS = 16;
 constexpr int QUANT_GROUPS = 4;            // groups of 4 warps take slabs round-robin
 constexpr int NUM_THREADS = (2 + QUANT_WARPS) * 32;
+constexpr int LUT_BYTES = 3200;            // code look-up table, see lut_row_offset
+
 
 template <int RP>
 struct Cfg {
   static constexpr int W_BYTES = SLAB_K * RP * 2;                 // lora_down slab
   static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
-  static constexpr int STAGES_RAW = (232448 - 1024 - 512) / STAGE_BYTES;
+  static constexpr int STAGES_RAW = (232448 - 1024 - 512 - LUT_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : (STAGES_RAW / 4) * 4;   // a multiple of the group count
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512;
+  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + LUT_BYTES;
   static constexpr int TMEM_COLS = RP < 32 ? 32 : RP;             // power of two >= 32
   static constexpr int EPI_COLS = RP / 4 < 32 ? 32 : RP / 4;      // accumulator columns per epilogue warp
   static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the ring");
@@ -94,10 +96,21 @@ __device__ __forceinline__ void unpack_group(const uint4& lo16, const uint4& hi1
   }
 }
 
+// Row J (1..15) of the code table starts here and holds 24 J + 13 entries:
+// entry m = how many of {1,3,5,7,10,14,20} * J are <= m.
+__host__ __device__ constexpr uint32_t lut_row_offset(uint32_t J) { return (J - 1u) * (12u * J + 13u); }
+static_assert(lut_row_offset(16) <= LUT_BYTES, "code table size");
+
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+  uint32_t v;
+  asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
 // One 16-element group (already widened to fp32): smoothing divide, amax, scale byte, eight code bytes.
 __device__ __forceinline__ void quantize_group(float (&f)[16], const float4* __restrict__ tb,
-                                               bool has_table, bool use_fdiv, uint32_t& code_lo, uint32_t& code_hi,
-                                               uint32_t& sbyte) {
+                                               bool has_table, bool use_fdiv, uint32_t lut_addr,
+                                               uint32_t& code_lo, uint32_t& code_hi, uint32_t& sbyte) {
   if (has_table) {
     if (!use_fdiv) {
 #pragma unroll
@@ -132,18 +145,38 @@ __device__ __forceinline__ void quantize_group(float (&f)[16], const float4* __r
   s = fminf(fmaxf(s, 1e-12f), 448.0f);
   const uint32_t sb = static_cast<uint32_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3));
   sbyte = sb;
-  float sf = e4m3_to_f32(static_cast<uint8_t>(sb));
-  // zero scale: every non-zero value saturates, zeros stay zero; 2^-147 * {.25 .. 5} are all
-  // positive and below any normal number
-  sf = (sf == 0.0f) ? __uint_as_float(4u) : sf;
-  GroupBounds gb;
-  gb.p[0] = sf * 0.25f; gb.p[1] = sf * 0.75f; gb.p[2] = sf * 1.25f; gb.p[3] = sf * 1.75f;
-  gb.p[4] = sf * 2.5f;  gb.p[5] = sf * 3.5f;  gb.p[6] = sf * 5.0f;
   uint32_t lo = 0, hi = 0;
+  if (sb != 0u && sb != 0x7Eu) {
+    // Table path.  scale = J * 2^E with J in 1..15, so |v| >= scale * b  <=>  floor(4 |v| 2^-E) >= J * (4b),
+    // 4b in {1,3,5,7,10,14,20}.  4 |v| 2^-E is an exact power-of-two scaling, the floor comes from an
+    // add of 2^23 rounded toward zero (its low mantissa bits are the integer), and the count of
+    // satisfied bounds is read from a per-J row of a shared-memory table.  Because the scale is
+    // amax/6 rounded to e4m3 by at most half a unit of J, the integer never exceeds 24 J + 12.
+    const uint32_t e = sb >> 3, m3 = sb & 7u;
+    const uint32_t J = e ? 8u + m3 : m3;
+    const float mult = __uint_as_float((e ? 139u - e : 138u) << 23);      // 2^(2 - E)
+    const float tmax = static_cast<float>(24u * J + 12u);
+    const uint32_t base = lut_addr + lut_row_offset(J) - 0x4B000000u;      // bits(2^23 + m) = 0x4B000000 + m
 #pragma unroll
-  for (int j = 0; j < 8; ++j) lo += e2m1_code(f[j], gb) << (4 * j);
+    for (int j = 0; j < 16; ++j) {
+      const float t = fminf(fabsf(f[j]) * mult, tmax);
+      const uint32_t idx = lds_u8(__float_as_uint(__fadd_rz(t, 8388608.0f)) + base);
+      const uint32_t sgn = (__float_as_uint(__fadd_rn(f[j], 0.0f)) >> 28) & 8u;   // -0.0 + 0.0 = +0.0
+      const uint32_t code = idx | sgn;
+      if (j < 8) lo += code << (4 * j); else hi += code << (4 * (j - 8));
+    }
+  } else {
+    // zero scale (everything non-zero saturates) or the 448 clamp (ratios are unbounded): compare path
+    float sf = e4m3_to_f32(static_cast<uint8_t>(sb));
+    sf = (sf == 0.0f) ? __uint_as_float(4u) : sf;     // 2^-147 * {.25 .. 5}: positive, below any normal number
+    GroupBounds gb;
+    gb.p[0] = sf * 0.25f; gb.p[1] = sf * 0.75f; gb.p[2] = sf * 1.25f; gb.p[3] = sf * 1.75f;
+    gb.p[4] = sf * 2.5f;  gb.p[5] = sf * 3.5f;  gb.p[6] = sf * 5.0f;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) hi += e2m1_code(f[8 + j], gb) << (4 * j);
+    for (int j = 0; j < 8; ++j) lo += e2m1_code(f[j], gb) << (4 * j);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) hi += e2m1_code(f[8 + j], gb) << (4 * j);
+  }
   code_lo = lo; code_hi = hi;
 }
 
@@ -164,6 +197,8 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx ctx{abort_flag};
+  uint8_t* lut = smem + C::RING_BYTES + 512;
+  const uint32_t lut_addr = smem_u32(lut);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t ks = gridDim.y;               // cluster = (1, KS, 1): blockIdx.y is the rank along K
@@ -190,6 +225,13 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
+  }
+  // code table: row J, entry m -> #{ n in {1,3,5,7,10,14,20} : n * J <= m }
+  for (uint32_t J = 1 + (threadIdx.x >> 6); J <= 15; J += NUM_THREADS >> 6) {
+    for (uint32_t m = threadIdx.x & 63u; m < 24u * J + 13u; m += 64u) {
+      const uint32_t c = (1u * J <= m) + (3u * J <= m) + (5u * J <= m) + (7u * J <= m) + (10u * J <= m) + (14u * J <= m) + (20u * J <= m);
+      lut[lut_row_offset(J) + m] = static_cast<uint8_t>(c);
+    }
   }
   // out-of-range smooth anywhere in K (flag word behind the table) selects the IEEE divide
   const bool use_fdiv = has_table && reinterpret_cast<const uint32_t*>(p.table + p.K)[0] != 0u;
@@ -285,7 +327,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       for (int rr = 0; rr < 2; ++rr) {
         const int row = lane + 32 * rr;
         uint32_t clo, chi, sb;
-        quantize_group(f[rr], tb, has_table, use_fdiv, clo, chi, sb);
+        quantize_group(f[rr], tb, has_table, use_fdiv, lut_addr, clo, chi, sb);
         if ((p.dbg & 32) && clo != 0x12345678u) continue;
         *reinterpret_cast<uint2*>(act_base + static_cast<size_t>(row) * (p.K >> 1) + (k0 >> 1)) = make_uint2(clo, chi);
         p.scales[static_cast<size_t>(gi) * p.M_pad + m0 + row] = static_cast<uint8_t>(sb);
