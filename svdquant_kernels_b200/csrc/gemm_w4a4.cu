@@ -9,19 +9,19 @@
 // The reference's own kernel for this op is
 // cute_kernels/gemm_w4a4/kernel_v2_fa4.py:841-1589.
 //
-// Work decomposition (320 threads per CTA, one CTA per SM):
+// Work decomposition (384 threads per CTA, one CTA per SM):
 //   warps 0-7  epilogue: tensor memory -> registers -> affine -> 16 bit ->
 //              swizzled shared memory -> TMA store (a 32-row x BN/2 strip per warp)
 //   warp  8    producer: TMA loads into a ring of shared-memory stages
-//   warp  9    MMA issuer: per slab the tcgen05.cp copies of the stage's scale
-//              atoms into tensor memory, then the four tcgen05.mma, then commits
-// Copies and MMAs issued by one thread execute in issue order on the same
-// pipe, so the scale copies need no barrier of their own: the MMAs that follow
-// see the scales, and the copies of the slab after next cannot overtake the
-// MMAs still reading the buffer they overwrite.  Measured on a B200, a slab's
-// 12 copies + 4 MMAs issued this way keep the pipe at 128 cycles per 256 x 256
-// x 64 MMA, the rate of the MMAs alone.  Single-lane roles stay converged and
-// elect one lane per slab, so descriptors and addresses live in uniform registers.
+//   warp  9    MMA issuer: tcgen05.mma + commits
+//   warps 10-11 scale copiers: tcgen05.cp of the stage's scale atoms into a
+//              multi-buffered scale area of tensor memory, a few slabs ahead;
+//              each warp takes two of the slab's four k-blocks
+// Issuing one tcgen05 instruction costs tens of cycles of a single thread, and a
+// 256-wide slab needs 12 scale copies next to its 4 MMAs, so the two kinds are
+// issued by different warps and handshake through mbarriers.  All
+// single-lane roles stay converged and elect one lane per instruction, so
+// descriptors and addresses live in uniform registers.
 //
 // CG = 1: a CTA computes a 128 x BN tile.
 // CG = 2: two CTAs of a cluster compute a 256 x BN tile with cta_group::2
@@ -59,7 +59,8 @@ constexpr int BK = 256;          // K elements per stage (128 bytes of codes per
 constexpr int A_BYTES = BM * 128;
 constexpr int SFA_BYTES = BM * (BK / 16);  // 2048
 constexpr int EPI_WARPS = 8;
-constexpr int NUM_THREADS = (EPI_WARPS + 2) * 32;
+constexpr int SF_WARPS = 2;       // scale copiers: each takes two of a slab's four k-blocks
+constexpr int NUM_THREADS = (EPI_WARPS + 2 + SF_WARPS) * 32;
 constexpr int STORE_BUF_BYTES = 32 * 128;  // one 32-row x 64-column strip of y
 
 template <int CG, int BN>
@@ -81,14 +82,15 @@ struct Cfg {
   static constexpr int SFA_COLS = 16;                 // 4 k-blocks x 4 columns
   static constexpr int SFB_COLS = 4 * (BN / 32);      // 4 k-blocks x BN/32 columns
   static constexpr int SF_COLS = SFA_COLS + SFB_COLS; // one scale buffer
-  // Two alternating scale buffers in tensor memory (in-order execution would allow one; the second
-  // costs 48 columns nobody else needs).
-  static constexpr int SF_BUFS = 2;
+  // Scale buffers in tensor memory.  Copies and MMAs execute in issue order on one pipe, and an MMA
+  // may only be issued once its scales have landed, so the copier has to run several slabs ahead of
+  // the MMA issuer or every slab pays a copy + wake-up bubble.
+  static constexpr int SF_BUFS = (ACC_STAGES * BN + 4 * SF_COLS <= 512) ? 4 : 2;
   static constexpr int TMEM_COLS = 512;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STORE_BYTES + TAIL_BYTES;
   static_assert(ACC_STAGES * BN + SF_BUFS * SF_COLS <= TMEM_COLS, "tensor memory budget");
   static_assert(STAGES >= 3, "ring too shallow");
-  static_assert((2 * STAGES + 2 * ACC_STAGES) * 8 + 16 <= 256, "barrier block");
+  static_assert((2 * STAGES + 2 * ACC_STAGES + 2 * SF_BUFS) * 8 + 16 <= 256, "barrier block");
 };
 
 struct Params {
@@ -144,11 +146,20 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* empty = bars + C::STAGES;                             // [STAGES]     stage consumed by the MMAs (per CTA)
   uint64_t* acc_full = bars + 2 * C::STAGES;                      // [ACC_STAGES] accumulator complete (per CTA)
   uint64_t* acc_empty = acc_full + C::ACC_STAGES;                 // [ACC_STAGES] accumulator drained (leader's copy is used)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + C::ACC_STAGES);
+  uint64_t* sf_full = acc_empty + C::ACC_STAGES;                  // [SF_BUFS] scale buffer copied (leader CTA)
+  uint64_t* sf_empty = sf_full + C::SF_BUFS;                      // [SF_BUFS] scale buffer consumed by the MMAs (leader CTA)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + C::SF_BUFS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx ctx{abort_flag};
+  // bounded wait whose verdict is the same in all lanes of the calling (converged) warp
+  auto uwait = [&](uint64_t* bar, uint32_t parity, const WaitCtx& c, unsigned int code, unsigned int tag) -> bool {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, c, code, tag)) != 0;
+  };
 
-  const int warp = threadIdx.x >> 5;
+  // The warp index is taken through a shuffle so that the compiler can prove it warp-uniform: only
+  // then do the role branches below count as convergent code, where descriptors and addresses stay
+  // in uniform registers.  Single-lane roles also vote on every wait result for the same reason.
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0);
   const int lane = threadIdx.x & 31;
   const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;      // 0 = leader of the pair
   const int pair = blockIdx.x / CG;
@@ -158,6 +169,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     *abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int a = 0; a < C::ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EPI_WARPS * CG); }
+    for (int b = 0; b < C::SF_BUFS; ++b) { mbar_init(&sf_full[b], SF_WARPS); mbar_init(&sf_empty[b], 1); }
     fence_barrier_init();
   }
   if (warp == EPI_WARPS && lane == 0) {
@@ -195,7 +207,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int nrow0 = n0 + rank * C::B_ROWS;
       for (int kt = 0; kt < kt_all; ++kt, ++it) {
         const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, it)) { ok = false; break; }
+        if (!uwait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, it)) { ok = false; break; }
         uint8_t* st = smem + s * C::STAGE_BYTES;
         // Codes past K are zero-filled by TMA.  The scale atoms of a (128-row block, slab) are four
         // consecutive 512-byte rows of the swizzled scale buffer seen as a [blocks * K/64, 512 B] matrix;
@@ -232,45 +244,38 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ------------------------------ MMA issuer (leader CTA only) ------------------------------
     if (rank == 0) {
       constexpr uint64_t kDescAB = smem_desc_base(0, 1024, kSwizzle128B);   // K-major, 8-row groups 1024 B apart
-      constexpr uint64_t kDescSF = smem_desc_base(0, 128, kSwizzleNone);    // 8 x 16 B core matrices, 128 B apart
       constexpr uint32_t kIdescMain = idesc_nvfp4(BM * CG, BN);
       constexpr uint32_t kIdescLora = idesc_f16(kBf16, kBf16, BM * CG, BN, false, false);
       constexpr uint16_t kMask = (CG == 2) ? 3 : 1;
-      uint32_t it = 0, tcount = 0;
+      uint32_t it = 0, tcount = 0, sf_it = 0;
       bool ok = true;
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++tcount) {
         const uint32_t as = tcount % C::ACC_STAGES, aph = (tcount / C::ACC_STAGES) & 1;
-        if (!(p.dbg & 32) && !mbar_wait(&acc_empty[as], aph ^ 1, ctx, kDevWaitAccFree, tcount)) { ok = false; break; }
+        if (!(p.dbg & 32) && !uwait(&acc_empty[as], aph ^ 1, ctx, kDevWaitAccFree, tcount)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + as * BN;
         for (int kt = 0; kt < kt_all; ++kt, ++it) {
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
-          if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, it)) { ok = false; break; }
-          tc_fence_after_sync();
+          if (!uwait(&full[s], ph, ctx, kDevWaitFull, it)) { ok = false; break; }
           const bool main_slab = kt < kt_main;
+          const uint32_t sb = sf_it % C::SF_BUFS;
+          if (main_slab && !(p.dbg & 4)) {
+            if (!uwait(&sf_full[sb], (sf_it / C::SF_BUFS) & 1, ctx, kDevWaitMisc, it)) { ok = false; break; }
+          }
+          tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
-          const uint32_t sfa_addr = b_addr + C::B_BYTES, sfb_addr = sfa_addr + SFA_BYTES;
-          const uint32_t tsfa = tmem_sf + (it % C::SF_BUFS) * C::SF_COLS, tsfb = tsfa + C::SFA_COLS;
+          const uint32_t tsfa = tmem_sf + sb * C::SF_COLS, tsfb = tsfa + C::SFA_COLS;
           const int nkb = (p.dbg & 4) ? 0 : (main_slab ? min(4, k_groups4 - kt * 4)
                                                         : min(4, (p.R - ((kt - kt_main) % lora_slabs) * 64) / 16));
           if (elect_one()) {
             if (main_slab) {
-              // this slab's scale atoms: per k-block one copy for the 128 rows of A (in each CTA) and
-              // BN/128 copies for the columns of B
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                if (j < nkb) {
-                  tmem_cp_scales<CG>(tsfa + j * 4, smem_desc(kDescSF, sfa_addr + j * 512));
-#pragma unroll
-                  for (int h = 0; h < BN / 128; ++h)
-                    tmem_cp_scales<CG>(tsfb + j * (BN / 32) + h * 4, smem_desc(kDescSF, sfb_addr + h * 2048 + j * 512));
-                }
 #pragma unroll
               for (int j = 0; j < 4; ++j)
                 if (j < nkb)
                   mma_nvfp4<CG>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
                                 kIdescMain, tsfa + j * 4, tsfb + j * (BN / 32), (kt | j) != 0 ? 1u : 0u);
+              if (!(p.dbg & 4)) tc_commit_local<CG>(&sf_empty[sb]);   // scale buffer reusable once these MMAs are done
             } else {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
@@ -278,10 +283,52 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                   mma_f16<CG>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
                               kIdescLora, (kt | j) != 0 ? 1u : 0u);
             }
-            tc_commit_mask<CG>(&empty[s], kMask);          // stage reusable (in both CTAs) once these copies and MMAs have read it
+            tc_commit_mask<CG>(&empty[s], kMask);          // stage reusable (in both CTAs) once these MMAs have read it
             if (kt == kt_all - 1) tc_commit_mask<CG>(&acc_full[as], kMask);   // accumulator complete
           }
           __syncwarp();
+          if (main_slab) ++sf_it;
+        }
+      }
+    }
+  } else if (warp >= EPI_WARPS + 2) {
+    // ------------------------------ scale copiers (leader CTA only) ------------------------------
+    // Copies the scale atoms of main slab n into scale buffer n % SF_BUFS, up to SF_BUFS - 1 slabs ahead of the MMAs.
+    if (rank == 0 && !(p.dbg & 4)) {
+      constexpr uint64_t kDescSF = smem_desc_base(0, 128, kSwizzleNone);    // 8 x 16 B core matrices, 128 B apart
+      const int jlo = (warp - (EPI_WARPS + 2)) * (4 / SF_WARPS);            // this warp's k-blocks: jlo, jlo + 1
+      uint32_t it = 0, sf_it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+        for (int kt = 0; kt < kt_all; ++kt, ++it) {
+          // Every slab's barrier is waited on in order, LoRA slabs (which carry no scales) included: a
+          // waiter that skipped ahead could get two ring revolutions in front of the producer, where the
+          // parity of a barrier no longer tells the revolutions apart.
+          const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
+          if (!uwait(&full[s], ph, ctx, kDevWaitFull, 0x20000 + it)) { ok = false; break; }
+          if (kt >= kt_main) continue;
+          const uint32_t sb = sf_it % C::SF_BUFS;
+          if (!uwait(&sf_empty[sb], ((sf_it / C::SF_BUFS) & 1) ^ 1, ctx, kDevWaitMisc, 0x20000 + it)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sfa_addr = smem_u32(smem + s * C::STAGE_BYTES) + A_BYTES + C::B_BYTES;
+          const uint32_t sfb_addr = sfa_addr + SFA_BYTES;
+          const uint32_t tsfa = tmem_sf + sb * C::SF_COLS, tsfb = tsfa + C::SFA_COLS;
+          const int nkb = min(4, k_groups4 - kt * 4);
+          if (elect_one()) {
+#pragma unroll
+            for (int jj = 0; jj < 4 / SF_WARPS; ++jj) {
+              const int j = jlo + jj;
+              if (j < nkb && !((p.dbg & 2) && kt > 0)) {
+                tmem_cp_scales<CG>(tsfa + j * 4, smem_desc(kDescSF, sfa_addr + j * 512));
+#pragma unroll
+                for (int h = 0; h < BN / 128; ++h)
+                  tmem_cp_scales<CG>(tsfb + j * (BN / 32) + h * 4, smem_desc(kDescSF, sfb_addr + h * 2048 + j * 512));
+              }
+            }
+            tc_commit_local<CG>(&sf_full[sb]);
+          }
+          __syncwarp();
+          ++sf_it;
         }
       }
     }
