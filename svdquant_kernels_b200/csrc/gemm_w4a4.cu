@@ -17,9 +17,10 @@
 //   warps 10-11 scale copiers: tcgen05.cp of the stage's scale atoms into a
 //              multi-buffered scale area of tensor memory, a few slabs ahead;
 //              each warp takes two of the slab's four k-blocks
-// Issuing one tcgen05 instruction costs tens of cycles of a single thread, and a
-// 256-wide slab needs 12 scale copies next to its 4 MMAs, so the two kinds are
-// issued by different warps and handshake through mbarriers.  All
+// Issuing one tcgen05.cp costs its thread about 30 cycles (measured), and a
+// 256-wide slab needs 12 scale copies next to its 4 MMAs, which together with
+// the waits is more than the 512 cycles the slab's MMAs run for; so the two
+// kinds are issued by different warps and handshake through mbarriers.  All
 // single-lane roles stay converged and elect one lane per instruction, so
 // descriptors and addresses live in uniform registers.
 //
@@ -85,7 +86,8 @@ struct Cfg {
   // Scale buffers in tensor memory.  Copies and MMAs execute in issue order on one pipe, and an MMA
   // may only be issued once its scales have landed, so the copier has to run several slabs ahead of
   // the MMA issuer or every slab pays a copy + wake-up bubble.
-  static constexpr int SF_BUFS = (ACC_STAGES * BN + 4 * SF_COLS <= 512) ? 4 : 2;
+  static constexpr int SF_BUFS_FIT = (512 - ACC_STAGES * BN) / SF_COLS;
+  static constexpr int SF_BUFS = SF_BUFS_FIT > 6 ? 6 : SF_BUFS_FIT;
   static constexpr int TMEM_COLS = 512;
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STORE_BYTES + TAIL_BYTES;
   static_assert(ACC_STAGES * BN + SF_BUFS * SF_COLS <= TMEM_COLS, "tensor memory budget");
