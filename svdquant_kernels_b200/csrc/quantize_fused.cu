@@ -10,8 +10,8 @@
 // Decomposition.  A cluster of KS (1 or 2) CTAs owns one tile of 64 rows; CTA k
 // owns a contiguous range of 64-column slabs of K.  Per slab the producer warp
 // TMA-loads the x tile (64 x 64, 128-byte swizzle) and the matching lora_down
-// slab (64 x R) into one ring stage; the {smooth, 1/smooth} table is read
-// straight from global memory (it is 8 bytes per column and L2-resident).
+// slab (64 x R) into one ring stage, together with the slab's 64 entries of
+// the {smooth, 1/smooth} table (a 512-byte bulk copy).
 // Two consumers read the stage: the MMA warp accumulates x_tile @ lora_down_slab
 // into a [64 x R] fp32 accumulator in tensor memory, and sixteen quantize warps
 // turn the tile into codes and scales.  x is read from HBM exactly once.  With
@@ -41,24 +41,29 @@ namespace qf {
 constexpr int TILE_M = 64;
 constexpr int SLAB_K = 64;                 // columns per ring stage (128 bytes of 16-bit x)
 constexpr int X_BYTES = TILE_M * 128;      // 8 KB
-constexpr int QUANT_WARPS = 16;
-constexpr int QUANT_GROUPS = 4;            // groups of 4 warps take slabs round-robin
+constexpr int QUANT_GROUPS = 6;            // groups of 4 warps take slabs round-robin
+constexpr int QUANT_WARPS = 4 * QUANT_GROUPS;
 constexpr int NUM_THREADS = (2 + QUANT_WARPS) * 32;
-constexpr int LUT_BYTES = 3200;            // code look-up table, see lut_row_offset
+constexpr int LUT_ROW_BYTES = 3075;        // code look-up table, see lut_row_offset
+constexpr int LUT_COPIES = 4;              // lane l reads copy l % 4; consecutive copies are 8 banks apart
+constexpr int LUT_STRIDE = 3104;           // 24 * 128 + 32
+constexpr int LUT_BYTES = LUT_COPIES * LUT_STRIDE;
+constexpr int TB_BYTES = SLAB_K * 8;       // {smooth, 1/smooth} of a slab's columns
+constexpr int TB_GROUP_STRIDE = 144;       // spacing of the four 128-byte group pieces in a stage
 
 
 template <int RP>
 struct Cfg {
   static constexpr int W_BYTES = SLAB_K * RP * 2;                 // lora_down slab
-  static constexpr int STAGE_BYTES = X_BYTES + W_BYTES;
+  static constexpr int STAGE_BYTES = X_BYTES + W_BYTES + 1024;   // table slab + padding to the 1 KB the swizzled tiles need
   static constexpr int STAGES_RAW = (232448 - 1024 - 512 - LUT_BYTES) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : (STAGES_RAW / 4) * 4;   // a multiple of the group count
+  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + LUT_BYTES;
   static constexpr int TMEM_COLS = RP < 32 ? 32 : RP;             // power of two >= 32
   static constexpr int EPI_COLS = RP / 4 < 32 ? 32 : RP / 4;      // accumulator columns per epilogue warp
   static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the ring");
-  static_assert(STAGES >= 4 && STAGES % QUANT_GROUPS == 0, "ring depth");
+  static_assert(STAGES >= 4, "ring depth");
 };
 
 struct Params {
@@ -99,7 +104,7 @@ __device__ __forceinline__ void unpack_group(const uint4& lo16, const uint4& hi1
 // Row J (1..15) of the code table starts here and holds 24 J + 13 entries:
 // entry m = how many of {1,3,5,7,10,14,20} * J are <= m.
 __host__ __device__ constexpr uint32_t lut_row_offset(uint32_t J) { return (J - 1u) * (12u * J + 13u); }
-static_assert(lut_row_offset(16) <= LUT_BYTES, "code table size");
+static_assert(lut_row_offset(16) <= LUT_ROW_BYTES && LUT_ROW_BYTES <= LUT_STRIDE, "code table size");
 
 __device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
   uint32_t v;
@@ -107,29 +112,31 @@ __device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
   return v;
 }
 
-// One 16-element group (already widened to fp32): smoothing divide, amax, scale byte, eight code bytes.
-__device__ __forceinline__ void quantize_group(float (&f)[16], const float4* __restrict__ tb,
-                                               bool has_table, bool use_fdiv, uint32_t lut_addr,
-                                               uint32_t& code_lo, uint32_t& code_hi, uint32_t& sbyte) {
-  if (has_table) {
-    if (!use_fdiv) {
+// Smoothing divide of one 16-element group (already widened to fp32); tb points at the group's
+// eight {s0, r0, s1, r1} table entries in shared memory (the same address in every lane).
+__device__ __forceinline__ void smooth_divide(float (&f)[16], const float4* tb, bool use_fdiv) {
+  if (!use_fdiv) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 t = tb[j];          // {s0, r0, s1, r1}
-        const float q0 = f[2 * j] * t.y;
-        f[2 * j] = fmaf(fmaf(-t.x, q0, f[2 * j]), t.y, q0);
-        const float q1 = f[2 * j + 1] * t.w;
-        f[2 * j + 1] = fmaf(fmaf(-t.z, q1, f[2 * j + 1]), t.w, q1);
-      }
-    } else {
+    for (int j = 0; j < 8; ++j) {
+      const float4 t = tb[j];          // {s0, r0, s1, r1}
+      const float q0 = f[2 * j] * t.y;
+      f[2 * j] = fmaf(fmaf(-t.x, q0, f[2 * j]), t.y, q0);
+      const float q1 = f[2 * j + 1] * t.w;
+      f[2 * j + 1] = fmaf(fmaf(-t.z, q1, f[2 * j + 1]), t.w, q1);
+    }
+  } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 t = tb[j];
-        f[2 * j] = __fdiv_rn(f[2 * j], t.x);
-        f[2 * j + 1] = __fdiv_rn(f[2 * j + 1], t.z);
-      }
+    for (int j = 0; j < 8; ++j) {
+      const float4 t = tb[j];
+      f[2 * j] = __fdiv_rn(f[2 * j], t.x);
+      f[2 * j + 1] = __fdiv_rn(f[2 * j + 1], t.z);
     }
   }
+}
+
+// One 16-element group (smoothed, fp32): amax, scale byte, eight code bytes.
+__device__ __forceinline__ void quantize_group(float (&f)[16], uint32_t lut_addr,
+                                               uint32_t& code_lo, uint32_t& code_hi, uint32_t& sbyte) {
   float m0 = fmaxf(fabsf(f[0]), fabsf(f[1])), m1 = fmaxf(fabsf(f[2]), fabsf(f[3]));
   float m2 = fmaxf(fabsf(f[4]), fabsf(f[5])), m3 = fmaxf(fabsf(f[6]), fabsf(f[7]));
 #pragma unroll
@@ -198,14 +205,18 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx ctx{abort_flag};
   uint8_t* lut = smem + C::RING_BYTES + 512;
-  const uint32_t lut_addr = smem_u32(lut);
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // warp index through a shuffle: provably warp-uniform, so the role branches are convergent code
+  const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
+  auto uwait = [&](uint64_t* bar, uint32_t parity, unsigned int code, unsigned int tag) -> bool {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, ctx, code, tag)) != 0;
+  };
   const uint32_t ks = gridDim.y;               // cluster = (1, KS, 1): blockIdx.y is the rank along K
   const uint32_t krank = blockIdx.y;
   const int m0 = blockIdx.x * TILE_M;
   const bool has_lora = p.R > 0;
   const bool has_table = p.table != nullptr;
+  const uint32_t lut_addr = smem_u32(lut) + (lane & 3) * LUT_STRIDE;
 
   // slabs owned by this CTA
   const int n_slabs = p.K / SLAB_K;
@@ -230,7 +241,8 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   for (uint32_t J = 1 + (threadIdx.x >> 6); J <= 15; J += NUM_THREADS >> 6) {
     for (uint32_t m = threadIdx.x & 63u; m < 24u * J + 13u; m += 64u) {
       const uint32_t c = (1u * J <= m) + (3u * J <= m) + (5u * J <= m) + (7u * J <= m) + (10u * J <= m) + (14u * J <= m) + (20u * J <= m);
-      lut[lut_row_offset(J) + m] = static_cast<uint8_t>(c);
+#pragma unroll
+      for (int cp = 0; cp < LUT_COPIES; ++cp) lut[cp * LUT_STRIDE + lut_row_offset(J) + m] = static_cast<uint8_t>(c);
     }
   }
   // out-of-range smooth anywhere in K (flag word behind the table) selects the IEEE divide
@@ -242,10 +254,10 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
-    const uint32_t stage_bytes = X_BYTES + (has_lora ? C::W_BYTES : 0);
+    const uint32_t stage_bytes = X_BYTES + (has_lora ? C::W_BYTES : 0) + (has_table ? TB_BYTES : 0);
     for (int i = 0; i < my_slabs; ++i) {
       const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
-      if (!mbar_wait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, i)) break;
+      if (!uwait(&empty[s], ph ^ 1, kDevWaitEmpty, i)) break;
       uint8_t* st = smem + s * C::STAGE_BYTES;
       const int k0 = k_begin + i * SLAB_K;
       if (elect_one()) {
@@ -254,6 +266,13 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         if (has_lora) {
 #pragma unroll
           for (int b = 0; b < RP / 64; ++b) tma_load_2d(st + X_BYTES + b * (SLAB_K * 128), &tmW, b * 64, k0, &full[s]);
+        }
+        if (has_table) {
+          // one 128-byte piece per 16-column group, 144 bytes apart: the four groups a quad of lanes
+          // reads at once then sit in different banks
+#pragma unroll
+          for (int gq = 0; gq < 4; ++gq)
+            bulk_load_1d(st + X_BYTES + C::W_BYTES + gq * TB_GROUP_STRIDE, p.table + k0 + gq * 16, 128, &full[s]);
         }
       }
       __syncwarp();
@@ -266,7 +285,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     bool ok = true;
     for (int i = 0; i < my_slabs && ok; ++i) {
       const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
-      if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, i)) { ok = false; break; }
+      if (!uwait(&full[s], ph, kDevWaitFull, i)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
       const uint32_t b_addr = a_addr + X_BYTES;
@@ -284,27 +303,25 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     }
   } else {
     // ------------------------------ quantize warps ------------------------------
-    const int qw = warp - 2;                  // 0..15
-    const int grp = qw >> 2;                  // takes slabs grp, grp + 4, ...
-    const int g = qw & 3;                     // 16-column group inside the slab
+    // Group grp takes slabs grp, grp + QUANT_GROUPS, ...; its warp wq owns rows 16 wq .. 16 wq + 15 of the
+    // tile.  Lane l works on 16-column group l % 4 of rows l / 4 and l / 4 + 8 of those, so the four
+    // lanes of a quad hold one row's whole 64-column stretch of the slab: their 8-byte code stores
+    // fill one 32-byte sector, and their scale bytes are adjacent in the atom layout.
+    const int qw = warp - 2;
+    const int grp = qw >> 2;
+    const int wq = qw & 3;
+    const int g = lane & 3;                   // 16-column group inside the slab
+    const int row_base = 16 * wq + (lane >> 2);
     const int groups = p.K >> 4;
     uint8_t* const act_base = p.act + static_cast<size_t>(m0) * (p.K >> 1);
     for (int i = grp; i < my_slabs; i += QUANT_GROUPS) {
       const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
-      // {smooth, 1/smooth} of this warp's 16 columns: the same address in every lane, read through
-      // the read-only path before the wait so that its latency hides behind the barrier
-      float4 tb[8];
-      if (has_table) {
-        const float4* tsrc = reinterpret_cast<const float4*>(p.table + k_begin + i * SLAB_K + g * 16);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) tb[j] = __ldg(tsrc + j);
-      }
       if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, 0x10000 + i)) break;
       const uint8_t* st = smem + s * C::STAGE_BYTES;
       uint4 raw[2][2];
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
-        const uint32_t row = lane + 32 * rr;
+        const uint32_t row = row_base + 8 * rr;
         const uint8_t* xrow = st + row * 128;
         raw[rr][0] = *reinterpret_cast<const uint4*>(xrow + (((2 * g) ^ (row & 7)) << 4));
         raw[rr][1] = *reinterpret_cast<const uint4*>(xrow + (((2 * g + 1) ^ (row & 7)) << 4));
@@ -312,6 +329,12 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       float f[2][16];
       unpack_group<T>(raw[0][0], raw[0][1], f[0]);
       unpack_group<T>(raw[1][0], raw[1][1], f[1]);
+      if (has_table) {
+        // {smooth, 1/smooth} of this lane's 16 columns landed with the slab
+        const float4* tb = reinterpret_cast<const float4*>(st + X_BYTES + C::W_BYTES + g * TB_GROUP_STRIDE);
+        smooth_divide(f[0], tb, use_fdiv);
+        smooth_divide(f[1], tb, use_fdiv);
+      }
       // Hand the stage back.  The ring was read through the generic proxy and will be overwritten
       // through the async proxy (TMA); mbarrier arrivals are performed by a separate unit and do not
       // wait for earlier shared-memory loads, so without these fences the refill can overtake the reads.
@@ -325,9 +348,9 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       const int gi = k0 >> 4;
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
-        const int row = lane + 32 * rr;
+        const int row = row_base + 8 * rr;
         uint32_t clo, chi, sb;
-        quantize_group(f[rr], tb, has_table, use_fdiv, lut_addr, clo, chi, sb);
+        quantize_group(f[rr], lut_addr, clo, chi, sb);
         if ((p.dbg & 32) && clo != 0x12345678u) continue;
         *reinterpret_cast<uint2*>(act_base + static_cast<size_t>(row) * (p.K >> 1) + (k0 >> 1)) = make_uint2(clo, chi);
         p.scales[static_cast<size_t>(gi) * p.M_pad + m0 + row] = static_cast<uint8_t>(sb);
@@ -539,6 +562,7 @@ int launch_quantize_fused(const void* x, const void* lora_down, const void* smoo
                           float* lora_act, void* ascales_swz, void* lora_act16, int M, int K, int R, int M_pad,
                           int dtype, cudaStream_t stream) {
   if (!quantize_fused_supported(M, K, R, M_pad)) return SVDQ_ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(smooth_table) % 16 != 0) return SVDQ_ERR_ALIGN;   // bulk copies start on 16-byte boundaries
   qf::Params p;
   p.table = static_cast<const float2*>(smooth_table);
   p.act = static_cast<uint8_t*>(act);

@@ -107,6 +107,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Same test, but the thread may be suspended by the hardware for up to about `hint_ns` while the
+// phase is incomplete (it is woken when the phase completes), instead of polling.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 #ifndef SVDQ_WAIT_LIMIT_NS
 #define SVDQ_WAIT_LIMIT_NS 400000000ull  // 0.4 s: orders of magnitude above any legitimate wait here
 #endif
@@ -119,9 +133,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   unsigned long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
     if (*ctx.abort_flag) return false;
-    if ((++spins & 0xFF) == 0) {
+    if ((++spins & 0x3F) == 0) {
       unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > SVDQ_WAIT_LIMIT_NS) {
