@@ -44,10 +44,6 @@ constexpr int X_BYTES = TILE_M * 128;      // 8 KB
 constexpr int QUANT_GROUPS = 6;            // groups of 4 warps take slabs round-robin
 constexpr int QUANT_WARPS = 4 * QUANT_GROUPS;
 constexpr int NUM_THREADS = (2 + QUANT_WARPS) * 32;
-constexpr int LUT_ROW_BYTES = 3075;        // code look-up table, see lut_row_offset
-constexpr int LUT_COPIES = 4;              // lane l reads copy l % 4; consecutive copies are 8 banks apart
-constexpr int LUT_STRIDE = 3104;           // 24 * 128 + 32
-constexpr int LUT_BYTES = LUT_COPIES * LUT_STRIDE;
 constexpr int TB_BYTES = SLAB_K * 8;       // {smooth, 1/smooth} of a slab's columns
 constexpr int TB_GROUP_STRIDE = 144;       // spacing of the four 128-byte group pieces in a stage
 
@@ -56,10 +52,10 @@ template <int RP>
 struct Cfg {
   static constexpr int W_BYTES = SLAB_K * RP * 2;                 // lora_down slab
   static constexpr int STAGE_BYTES = X_BYTES + W_BYTES + 1024;   // table slab + padding to the 1 KB the swizzled tiles need
-  static constexpr int STAGES_RAW = (232448 - 1024 - 512 - LUT_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES_RAW = (232448 - 1024 - 512) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + LUT_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512;
   static constexpr int TMEM_COLS = RP < 32 ? 32 : RP;             // power of two >= 32
   static constexpr int EPI_COLS = RP / 4 < 32 ? 32 : RP / 4;      // accumulator columns per epilogue warp
   static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the ring");
@@ -101,15 +97,11 @@ __device__ __forceinline__ void unpack_group(const uint4& lo16, const uint4& hi1
   }
 }
 
-// Row J (1..15) of the code table starts here and holds 24 J + 13 entries:
-// entry m = how many of {1,3,5,7,10,14,20} * J are <= m.
-__host__ __device__ constexpr uint32_t lut_row_offset(uint32_t J) { return (J - 1u) * (12u * J + 13u); }
-static_assert(lut_row_offset(16) <= LUT_ROW_BYTES && LUT_ROW_BYTES <= LUT_STRIDE, "code table size");
-
-__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
-  uint32_t v;
-  asm("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
+// Two floats -> two E2M1 codes in one byte (hi in bits 7-4, lo in bits 3-0), round to nearest, saturating.
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float hi, float lo) {
+  uint32_t d;
+  asm("{\n\t.reg .b8 r;\n\tcvt.rn.satfinite.e2m1x2.f32 r, %1, %2;\n\tcvt.u32.u8 %0, r;\n\t}" : "=r"(d) : "f"(hi), "f"(lo));
+  return d;
 }
 
 // Smoothing divide of one 16-element group (already widened to fp32); tb points at the group's
@@ -135,7 +127,7 @@ __device__ __forceinline__ void smooth_divide(float (&f)[16], const float4* tb, 
 }
 
 // One 16-element group (smoothed, fp32): amax, scale byte, eight code bytes.
-__device__ __forceinline__ void quantize_group(float (&f)[16], uint32_t lut_addr,
+__device__ __forceinline__ void quantize_group(float (&f)[16],
                                                uint32_t& code_lo, uint32_t& code_hi, uint32_t& sbyte) {
   float m0 = fmaxf(fabsf(f[0]), fabsf(f[1])), m1 = fmaxf(fabsf(f[2]), fabsf(f[3]));
   float m2 = fmaxf(fabsf(f[4]), fabsf(f[5])), m3 = fmaxf(fabsf(f[6]), fabsf(f[7]));
@@ -154,24 +146,34 @@ __device__ __forceinline__ void quantize_group(float (&f)[16], uint32_t lut_addr
   sbyte = sb;
   uint32_t lo = 0, hi = 0;
   if (sb != 0u && sb != 0x7Eu) {
-    // Table path.  scale = J * 2^E with J in 1..15, so |v| >= scale * b  <=>  floor(4 |v| 2^-E) >= J * (4b),
-    // 4b in {1,3,5,7,10,14,20}.  4 |v| 2^-E is an exact power-of-two scaling, the floor comes from an
-    // add of 2^23 rounded toward zero (its low mantissa bits are the integer), and the count of
-    // satisfied bounds is read from a per-J row of a shared-memory table.  Because the scale is
-    // amax/6 rounded to e4m3 by at most half a unit of J, the integer never exceeds 24 J + 12.
+    // Main path.  scale = J * 2^E with J in 1..15, so with t = 4 |v| / 2^E (an exact power-of-two
+    // scaling) the code is the number of n in {1,3,5,7,10,14,20} with n J <= t, i.e. with
+    // n J <= m = floor(t).  m comes from an add of 2^23 rounded toward zero.  m / (4 J) then lies
+    // on a bound n/4 exactly when m = n J and is at least 1/(4 J) away from every bound otherwise,
+    // so m * RN(1/(4 J)) * (1 + 2^-20) is strictly above the bound in the first case and on the
+    // right side of it in the second, and the hardware's float -> E2M1 conversion (round to
+    // nearest, saturating) of that product returns exactly the reference's code; checked
+    // exhaustively over J and m.  The conversion also carries the sign and packs two codes.
     const uint32_t e = sb >> 3, m3 = sb & 7u;
     const uint32_t J = e ? 8u + m3 : m3;
     const float mult = __uint_as_float((e ? 139u - e : 138u) << 23);      // 2^(2 - E)
-    const float tmax = static_cast<float>(24u * J + 12u);
-    const uint32_t base = lut_addr + lut_row_offset(J) - 0x4B000000u;      // bits(2^23 + m) = 0x4B000000 + m
+    const float rj = __fmul_rn(__frcp_rn(static_cast<float>(4u * J)), 1.00000095367431640625f);
+    uint32_t b[8];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float t = fminf(fabsf(f[j]) * mult, tmax);
-      const uint32_t idx = lds_u8(__float_as_uint(__fadd_rz(t, 8388608.0f)) + base);
-      const uint32_t sgn = (__float_as_uint(__fadd_rn(f[j], 0.0f)) >> 28) & 8u;   // -0.0 + 0.0 = +0.0
-      const uint32_t code = idx | sgn;
-      if (j < 8) lo += code << (4 * j); else hi += code << (4 * (j - 8));
+    for (int j = 0; j < 8; ++j) {
+      float w[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const float v = f[2 * j + h];
+        const float m = __fadd_rn(__fadd_rz(fabsf(v) * mult, 8388608.0f), -8388608.0f);
+        // sign of v with -0.0 counted as +0.0 (the reference tests v < 0)
+        const uint32_t sgn = __float_as_uint(__fadd_rn(v, 0.0f)) & 0x80000000u;
+        w[h] = __uint_as_float(__float_as_uint(__fmul_rn(m, rj)) | sgn);
+      }
+      b[j] = cvt_e2m1x2(w[1], w[0]);     // low nibble = even element
     }
+    lo = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
+    hi = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
   } else {
     // zero scale (everything non-zero saturates) or the 448 clamp (ratios are unbounded): compare path
     float sf = e4m3_to_f32(static_cast<uint8_t>(sb));
@@ -204,7 +206,6 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const WaitCtx ctx{abort_flag};
-  uint8_t* lut = smem + C::RING_BYTES + 512;
 
   // warp index through a shuffle: provably warp-uniform, so the role branches are convergent code
   const int warp = __shfl_sync(0xffffffffu, static_cast<int>(threadIdx.x >> 5), 0), lane = threadIdx.x & 31;
@@ -216,7 +217,6 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   const int m0 = blockIdx.x * TILE_M;
   const bool has_lora = p.R > 0;
   const bool has_table = p.table != nullptr;
-  const uint32_t lut_addr = smem_u32(lut) + (lane & 3) * LUT_STRIDE;
 
   // slabs owned by this CTA
   const int n_slabs = p.K / SLAB_K;
@@ -236,14 +236,6 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   if (warp == 1) {
     tmem_alloc(tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
-  }
-  // code table: row J, entry m -> #{ n in {1,3,5,7,10,14,20} : n * J <= m }
-  for (uint32_t J = 1 + (threadIdx.x >> 6); J <= 15; J += NUM_THREADS >> 6) {
-    for (uint32_t m = threadIdx.x & 63u; m < 24u * J + 13u; m += 64u) {
-      const uint32_t c = (1u * J <= m) + (3u * J <= m) + (5u * J <= m) + (7u * J <= m) + (10u * J <= m) + (14u * J <= m) + (20u * J <= m);
-#pragma unroll
-      for (int cp = 0; cp < LUT_COPIES; ++cp) lut[cp * LUT_STRIDE + lut_row_offset(J) + m] = static_cast<uint8_t>(c);
-    }
   }
   // out-of-range smooth anywhere in K (flag word behind the table) selects the IEEE divide
   const bool use_fdiv = has_table && reinterpret_cast<const uint32_t*>(p.table + p.K)[0] != 0u;
@@ -350,7 +342,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       for (int rr = 0; rr < 2; ++rr) {
         const int row = row_base + 8 * rr;
         uint32_t clo, chi, sb;
-        quantize_group(f[rr], lut_addr, clo, chi, sb);
+        quantize_group(f[rr], clo, chi, sb);
         if ((p.dbg & 32) && clo != 0x12345678u) continue;
         *reinterpret_cast<uint2*>(act_base + static_cast<size_t>(row) * (p.K >> 1) + (k0 >> 1)) = make_uint2(clo, chi);
         p.scales[static_cast<size_t>(gi) * p.M_pad + m0 + row] = static_cast<uint8_t>(sb);
