@@ -74,11 +74,15 @@ struct Params {
 };
 
 template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t v);
+// Both widen a pair after adding +0, which turns -0 into +0 and changes nothing else: the
+// reference gives a zero the sign bit only when the value tests < 0.
 template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
-  return __half22float2(*reinterpret_cast<__half2*>(&v));
+  return __half22float2(__hadd2(*reinterpret_cast<__half2*>(&v), __float2half2_rn(0.0f)));
 }
 template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
-  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+  const __nv_bfloat162 c = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&v), __float2bfloat162_rn(0.0f));
+  const uint32_t u = *reinterpret_cast<const uint32_t*>(&c);
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
 }
 
 // float4 slot of (row, c4) in the partial-accumulator buffer; the XOR spreads the
@@ -120,8 +124,8 @@ __device__ __forceinline__ void smooth_divide(float (&f)[16], const float4* tb, 
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float4 t = tb[j];
-      f[2 * j] = __fdiv_rn(f[2 * j], t.x);
-      f[2 * j + 1] = __fdiv_rn(f[2 * j + 1], t.z);
+      f[2 * j] = __fadd_rn(__fdiv_rn(f[2 * j], t.x), 0.0f);           // an underflow to -0 counts as +0
+      f[2 * j + 1] = __fadd_rn(__fdiv_rn(f[2 * j + 1], t.z), 0.0f);
     }
   }
 }
@@ -158,6 +162,7 @@ __device__ __forceinline__ void quantize_group(float (&f)[16],
     const uint32_t J = e ? 8u + m3 : m3;
     const float mult = __uint_as_float((e ? 139u - e : 138u) << 23);      // 2^(2 - E)
     const float rj = __fmul_rn(__frcp_rn(static_cast<float>(4u * J)), 1.00000095367431640625f);
+    const float c2 = -8388608.0f * rj;             // exact
     uint32_t b[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -165,10 +170,10 @@ __device__ __forceinline__ void quantize_group(float (&f)[16],
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const float v = f[2 * j + h];
-        const float m = __fadd_rn(__fadd_rz(fabsf(v) * mult, 8388608.0f), -8388608.0f);
-        // sign of v with -0.0 counted as +0.0 (the reference tests v < 0)
-        const uint32_t sgn = __float_as_uint(__fadd_rn(v, 0.0f)) & 0x80000000u;
-        w[h] = __uint_as_float(__float_as_uint(__fmul_rn(m, rj)) | sgn);
+        // (2^23 + m) * rj - 2^23 * rj in one fused operation is RN(m * rj); the sign bit of v rides along
+        // (v is never -0 here: inputs were made +0 and quotients cannot underflow in this path)
+        const float a = __fadd_rz(fabsf(v) * mult, 8388608.0f);
+        w[h] = __uint_as_float(__float_as_uint(fmaf(a, rj, c2)) | (__float_as_uint(v) & 0x80000000u));
       }
       b[j] = cvt_e2m1x2(w[1], w[0]);     // low nibble = even element
     }
@@ -442,6 +447,9 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 // [2^-60, 2^60] (or is NaN), where the three-step divide could over- or underflow.
 template <typename T>
 __global__ void smooth_table_kernel(const T* __restrict__ smooth, float2* __restrict__ table, int K) {
+  // upper bound: 2^60 for fp16 inputs; 2^16 for bf16 inputs, whose smallest subnormal (2^-133)
+  // divided by anything larger would underflow to a signed zero
+  constexpr float kMaxSmooth = std::is_same<T, __nv_bfloat16>::value ? 65536.0f : 1.1529215e18f;
   __shared__ int bad;
   if (threadIdx.x == 0) bad = 0;
   __syncthreads();
@@ -449,7 +457,7 @@ __global__ void smooth_table_kernel(const T* __restrict__ smooth, float2* __rest
     const float s = to_f32(smooth[i]);
     table[i] = make_float2(s, __frcp_rn(s));
     const float a = fabsf(s);
-    if (!(a >= 8.6736174e-19f && a <= 1.1529215e18f)) bad = 1;
+    if (!(a >= 8.6736174e-19f && a <= kMaxSmooth)) bad = 1;
   }
   __syncthreads();
   if (threadIdx.x == 0) *reinterpret_cast<uint2*>(table + K) = make_uint2(bad ? 1u : 0u, 0u);
