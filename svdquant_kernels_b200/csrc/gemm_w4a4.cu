@@ -187,6 +187,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   if constexpr (CG == 2) cluster_sync_all();   // both CTAs' barriers exist before anything remote touches them
   tc_fence_after_sync();
+  // Everything above touched only this CTA's shared and tensor memory, so it may overlap the tail of
+  // the kernel before this one in the stream; from here on its outputs are read.
+  pdl_trigger();
+  pdl_wait();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_sf = tmem_base + C::ACC_STAGES * BN;       // SF_BUFS buffers of [SFA 16 | SFB] columns
 
@@ -446,6 +450,12 @@ bool gemm_supported(int M, int N, int K, int R) {
   return M > 0 && N > 0 && K > 0 && M % 128 == 0 && N % 128 == 0 && K % 64 == 0 && R >= 0 && R % 16 == 0;
 }
 
+// TEMP switch: SVDQ_PDL=0 launches without programmatic serialization
+static bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("SVDQ_PDL"); return e == nullptr || atoi(e) != 0; }();
+  return on;
+}
+
 template <int CG, int BN, typename OutT>
 static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, const void* sfb, const void* la,
                          const void* lu, const void* wc, const void* bias, void* y, int M, int N, int K, int R,
@@ -485,11 +495,13 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   cfg.blockDim = dim3(gemm::NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CG; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, p) != cudaSuccess) return SVDQ_ERR_LAUNCH;
   return SVDQ_OK;
 }

@@ -41,7 +41,7 @@ namespace qf {
 constexpr int TILE_M = 64;
 constexpr int SLAB_K = 64;                 // columns per ring stage (128 bytes of 16-bit x)
 constexpr int X_BYTES = TILE_M * 128;      // 8 KB
-constexpr int QUANT_GROUPS = 6;            // groups of 4 warps take slabs round-robin
+constexpr int QUANT_GROUPS = 4;            // groups of 4 warps take slabs round-robin
 constexpr int QUANT_WARPS = 4 * QUANT_GROUPS;
 constexpr int NUM_THREADS = (2 + QUANT_WARPS) * 32;
 constexpr int TB_BYTES = SLAB_K * 8;       // {smooth, 1/smooth} of a slab's columns
@@ -53,13 +53,16 @@ struct Cfg {
   static constexpr int W_BYTES = SLAB_K * RP * 2;                 // lora_down slab
   static constexpr int STAGE_BYTES = X_BYTES + W_BYTES + 1024;   // table slab + padding to the 1 KB the swizzled tiles need
   static constexpr int STAGES_RAW = (232448 - 1024 - 512) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
+  // A multiple of the group count: a group then always meets the same stages, and the slab it waits
+  // for is the direct successor (in that stage) of one it consumed itself.  A one-bit phase parity
+  // cannot tell "one revolution behind" from "one ahead"; this rule makes the second impossible.
+  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : (STAGES_RAW / QUANT_GROUPS) * QUANT_GROUPS;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512;
   static constexpr int TMEM_COLS = RP < 32 ? 32 : RP;             // power of two >= 32
   static constexpr int EPI_COLS = RP / 4 < 32 ? 32 : RP / 4;      // accumulator columns per epilogue warp
   static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the ring");
-  static_assert(STAGES >= 4, "ring depth");
+  static_assert(STAGES >= QUANT_GROUPS && STAGES % QUANT_GROUPS == 0, "ring depth");
 };
 
 struct Params {
@@ -242,12 +245,15 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     tmem_alloc(tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
   }
-  // out-of-range smooth anywhere in K (flag word behind the table) selects the IEEE divide
-  const bool use_fdiv = has_table && reinterpret_cast<const uint32_t*>(p.table + p.K)[0] != 0u;
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_acc = *tmem_slot;
+  // set-up done; what follows reads and writes global memory
+  pdl_trigger();
+  pdl_wait();
+  // out-of-range smooth anywhere in K (flag word behind the table) selects the IEEE divide
+  const bool use_fdiv = has_table && reinterpret_cast<const uint32_t*>(p.table + p.K)[0] != 0u;
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
@@ -523,13 +529,15 @@ static int launch_qf(const void* x, const void* w, const qf::Params& p, cudaStre
   cfg.blockDim = dim3(qf::NUM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = ks;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  { const char* e = getenv("SVDQ_PDL"); cfg.numAttrs = (e == nullptr || atoi(e) != 0) ? 2 : 1; }
   if (cudaLaunchKernelEx(&cfg, kern, tmX, tmW, p) != cudaSuccess) return SVDQ_ERR_LAUNCH;
   return SVDQ_OK;
 }

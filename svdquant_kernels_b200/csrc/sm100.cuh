@@ -360,6 +360,17 @@ __device__ __forceinline__ void tc_commit_mask(uint64_t* bar, uint16_t cta_mask)
 }
 
 // ---------------------------------------------------------------------------
+// programmatic dependent launch
+// ---------------------------------------------------------------------------
+// A kernel launched with the programmatic-serialization attribute may start while the kernel before
+// it in the stream is still running; pdl_wait() returns once that kernel has completed and its
+// writes are visible (at once if there is no such kernel or the attribute was not set).
+// pdl_trigger() tells the runtime that the next such kernel may start being scheduled: its CTAs
+// take SMs as this grid's CTAs leave them and run their set-up up to their own pdl_wait().
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------
 // cluster helpers
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {

@@ -80,7 +80,9 @@ def test_against_reference_fixtures(name, force):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("M,K,R", [(64, 128, 16), (1, 64, 32), (300, 256, 32), (257, 1024, 128), (512, 3840, 128),
-                                   (700, 2560, 64), (130, 640, 256), (256, 192, 0)])
+                                   (700, 2560, 64), (130, 640, 256), (256, 192, 0),
+                                   # long K: every ring depth (it depends on R) goes through many revolutions
+                                   (256, 2560, 256), (200, 7680, 256), (192, 15360, 64), (128, 10240, 32)])
 def test_fused_matches_oracle(M, K, R, dtype):
     x, ld, sm = _inputs(M, K, R, dtype, 100 + M + K)
     _check(x, ld, sm, FUSED)
