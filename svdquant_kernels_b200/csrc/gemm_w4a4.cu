@@ -48,7 +48,6 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
-#include <cstdlib>
 #include <type_traits>
 
 namespace svdq {
@@ -100,7 +99,6 @@ struct Params {
   const void* bias;     // [N] or null
   int M, N, K, R;
   int tiles_m, tiles_n; // in units of (CG*128) x BN
-  int dbg;              // TEMP diagnostic switches
 };
 
 __device__ __forceinline__ uint32_t pack2(__half a, __half b) {
@@ -223,24 +221,20 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // the barrier that counts this CTA's bytes: its own for CG = 1, the leader's for a pair
         const uint32_t bar = (CG == 2) ? map_to_cta(smem_u32(&full[s]), 0) : smem_u32(&full[s]);
         if (elect_one()) {
-          if (p.dbg & 8) {
-            if (rank == 0) mbar_arrive(&full[s]);
-          } else {
-            if (rank == 0) mbar_arrive_expect_tx(&full[s], my_bytes * CG);
-            if (kt < kt_main) {
-              tma_load_2d_bar<CG>(st, &tmA, kt * 128, m0, bar);
-              tma_load_2d_bar<CG>(st + A_BYTES, &tmB, kt * 128, nrow0, bar);
-              tma_load_2d_bar<CG>(st + A_BYTES + C::B_BYTES, &tmSFA, 0, (mb * CG + rank) * k_groups4 + kt * 4, bar);
+          if (rank == 0) mbar_arrive_expect_tx(&full[s], my_bytes * CG);
+          if (kt < kt_main) {
+            tma_load_2d_bar<CG>(st, &tmA, kt * 128, m0, bar);
+            tma_load_2d_bar<CG>(st + A_BYTES, &tmB, kt * 128, nrow0, bar);
+            tma_load_2d_bar<CG>(st + A_BYTES + C::B_BYTES, &tmSFA, 0, (mb * CG + rank) * k_groups4 + kt * 4, bar);
 #pragma unroll
-              for (int h = 0; h < BN / 128; ++h)
-                tma_load_2d_bar<CG>(st + A_BYTES + C::B_BYTES + SFA_BYTES + h * 2048, &tmSFB, 0,
-                                    (nb * (BN / 128) + h) * k_groups4 + kt * 4, bar);
-            } else {
-              const int lt = kt - kt_main;
-              const int part = lt / lora_slabs, r0 = (lt % lora_slabs) * 64;
-              tma_load_2d_bar<CG>(st, &tmLA, r0, part * p.M + m0, bar);      // lora_act parts are stacked along rows
-              tma_load_2d_bar<CG>(st + A_BYTES, &tmLU, r0, nrow0, bar);
-            }
+            for (int h = 0; h < BN / 128; ++h)
+              tma_load_2d_bar<CG>(st + A_BYTES + C::B_BYTES + SFA_BYTES + h * 2048, &tmSFB, 0,
+                                  (nb * (BN / 128) + h) * k_groups4 + kt * 4, bar);
+          } else {
+            const int lt = kt - kt_main;
+            const int part = lt / lora_slabs, r0 = (lt % lora_slabs) * 64;
+            tma_load_2d_bar<CG>(st, &tmLA, r0, part * p.M + m0, bar);      // lora_act parts are stacked along rows
+            tma_load_2d_bar<CG>(st + A_BYTES, &tmLU, r0, nrow0, bar);
           }
         }
         __syncwarp();
@@ -257,7 +251,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++tcount) {
         const uint32_t as = tcount % C::ACC_STAGES, aph = (tcount / C::ACC_STAGES) & 1;
-        if (!(p.dbg & 32) && !uwait(&acc_empty[as], aph ^ 1, ctx, kDevWaitAccFree, tcount)) { ok = false; break; }
+        if (!uwait(&acc_empty[as], aph ^ 1, ctx, kDevWaitAccFree, tcount)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + as * BN;
         for (int kt = 0; kt < kt_all; ++kt, ++it) {
@@ -265,15 +259,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (!uwait(&full[s], ph, ctx, kDevWaitFull, it)) { ok = false; break; }
           const bool main_slab = kt < kt_main;
           const uint32_t sb = sf_it % C::SF_BUFS;
-          if (main_slab && !(p.dbg & 4)) {
+          if (main_slab) {
             if (!uwait(&sf_full[sb], (sf_it / C::SF_BUFS) & 1, ctx, kDevWaitMisc, it)) { ok = false; break; }
           }
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
           const uint32_t tsfa = tmem_sf + sb * C::SF_COLS, tsfb = tsfa + C::SFA_COLS;
-          const int nkb = (p.dbg & 4) ? 0 : (main_slab ? min(4, k_groups4 - kt * 4)
-                                                        : min(4, (p.R - ((kt - kt_main) % lora_slabs) * 64) / 16));
+          const int nkb = main_slab ? min(4, k_groups4 - kt * 4) : min(4, (p.R - ((kt - kt_main) % lora_slabs) * 64) / 16);
           if (elect_one()) {
             if (main_slab) {
 #pragma unroll
@@ -281,7 +274,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (j < nkb)
                   mma_nvfp4<CG>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
                                 kIdescMain, tsfa + j * 4, tsfb + j * (BN / 32), (kt | j) != 0 ? 1u : 0u);
-              if (!(p.dbg & 4)) tc_commit_local<CG>(&sf_empty[sb]);   // scale buffer reusable once these MMAs are done
+              tc_commit_local<CG>(&sf_empty[sb]);   // scale buffer reusable once these MMAs are done
             } else {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
@@ -300,7 +293,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp >= EPI_WARPS + 2) {
     // ------------------------------ scale copiers (leader CTA only) ------------------------------
     // Copies the scale atoms of main slab n into scale buffer n % SF_BUFS, up to SF_BUFS - 1 slabs ahead of the MMAs.
-    if (rank == 0 && !(p.dbg & 4)) {
+    if (rank == 0) {
       constexpr uint64_t kDescSF = smem_desc_base(0, 128, kSwizzleNone);    // 8 x 16 B core matrices, 128 B apart
       const int jlo = (warp - (EPI_WARPS + 2)) * (4 / SF_WARPS);            // this warp's k-blocks: jlo, jlo + 1
       uint32_t it = 0, sf_it = 0;
@@ -324,7 +317,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int jj = 0; jj < 4 / SF_WARPS; ++jj) {
               const int j = jlo + jj;
-              if (j < nkb && !((p.dbg & 2) && kt > 0)) {
+              if (j < nkb) {
                 tmem_cp_scales<CG>(tsfa + j * 4, smem_desc(kDescSF, sfa_addr + j * 512));
 #pragma unroll
                 for (int h = 0; h < BN / 128; ++h)
@@ -411,7 +404,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && !(p.dbg & 1)) {
+        if (lane == 0) {
           tma_store_2d(&tmY, buf, n0 + cbase, m0 + quarter * 32);
           tma_store_commit();
         }
@@ -450,12 +443,6 @@ bool gemm_supported(int M, int N, int K, int R) {
   return M > 0 && N > 0 && K > 0 && M % 128 == 0 && N % 128 == 0 && K % 64 == 0 && R >= 0 && R % 16 == 0;
 }
 
-// TEMP switch: SVDQ_PDL=0 launches without programmatic serialization
-static bool pdl_enabled() {
-  static const bool on = [] { const char* e = getenv("SVDQ_PDL"); return e == nullptr || atoi(e) != 0; }();
-  return on;
-}
-
 template <int CG, int BN, typename OutT>
 static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, const void* sfb, const void* la,
                          const void* lu, const void* wc, const void* bias, void* y, int M, int N, int K, int R,
@@ -480,7 +467,6 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   p.wc = wc; p.bias = bias;
   p.M = M; p.N = N; p.K = K; p.R = R;
   p.tiles_m = M / (gemm::BM * CG); p.tiles_n = N / BN;
-  { const char* e = getenv("SVDQ_DEBUG"); p.dbg = e ? atoi(e) : 0; }
   auto kern = gemm::gemm_w4a4_kernel<CG, BN, OutT>;
   static bool configured = false;
   if (!configured) {
@@ -501,7 +487,7 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  cfg.numAttrs = 2;
   if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, p) != cudaSuccess) return SVDQ_ERR_LAUNCH;
   return SVDQ_OK;
 }
@@ -522,10 +508,6 @@ int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, 
                      int M, int N, int K, int R, int dtype, int variant, cudaStream_t stream) {
   if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
   int cg, bn;
-  if (variant == 0) {
-    const char* e = getenv("SVDQ_GEMM_VARIANT");
-    if (e) variant = atoi(e);
-  }
   if (variant == 0) {
     cg = (M % 256 == 0) ? 2 : 1;
     bn = (N % 256 == 0) ? 256 : 128;

@@ -19,20 +19,34 @@
 // distributed shared memory: no atomics, no zero-fill, no scratch in global
 // memory.  (64-row tiles with pairs, not 128-row tiles with quads: a B200 keeps
 // at most 33 four-CTA clusters of this size resident, one short of the 34 row
-// tiles of a 4352-row activation, while 68 pairs fit in one wave.)
+// tiles of a 4352-row activation, while 68 pairs fit in one wave.  128-row tiles
+// whose K ranks meet through global memory were measured too: what they save in
+// lora_down traffic and MMA count, the 9 MB of partial sums that all CTAs write
+// at the same moment costs again.)
+//
+// Lane mapping.  The four lanes of a quad hold one row's four 16-column groups
+// of the slab, so their 8-byte code stores fill one 32-byte sector and their
+// scale bytes are adjacent in the atom layout; with a lane per row and a warp
+// per group the same stores touched 32 sectors each and cost 4 us more.
+//
+// Codes.  The scale byte is J * 2^E (J = 1..15), so floor(4 |v| / 2^E) is an
+// integer m and the E2M1 code is the number of n in {1,3,5,7,10,14,20} with
+// n J <= m.  m / (4 J) times (1 + 2^-20) is never on the wrong side of a
+// rounding bound of E2M1, so the hardware float -> E2M1 conversion of it
+// (cvt.rn.satfinite.e2m1x2.f32) yields exactly that count, with the sign, two
+// codes per instruction; see quantize_group.
 //
 // Exact arithmetic.  x / smooth must equal the IEEE quotient.  It is computed
 // as q0 = x*r, e = fma(-s, q0, x), q = fma(e, r, q0) with r = RN(1/s) from the
 // table; for operands with at most 11 significant bits this is the correctly
 // rounded quotient (checked exhaustively over mantissas), provided nothing
 // over- or underflows: the table builder raises a flag when a smooth value lies
-// outside [2^-60, 2^60] and the kernel then divides with __fdiv_rn.  amax / 6
+// outside [2^-60, 2^60] (2^16 for bf16) and the kernel then divides with __fdiv_rn.  amax / 6
 // uses the same three-step form (checked exhaustively as well).
 #include "nvfp4_math.cuh"
 #include "sm100.cuh"
 #include "svdq_internal.h"
 
-#include <cstdlib>
 #include <type_traits>
 
 namespace svdq {
@@ -41,7 +55,10 @@ namespace qf {
 constexpr int TILE_M = 64;
 constexpr int SLAB_K = 64;                 // columns per ring stage (128 bytes of 16-bit x)
 constexpr int X_BYTES = TILE_M * 128;      // 8 KB
-constexpr int QUANT_GROUPS = 4;            // groups of 4 warps take slabs round-robin
+#ifndef SVDQ_QUANT_GROUPS
+#define SVDQ_QUANT_GROUPS 4
+#endif
+constexpr int QUANT_GROUPS = SVDQ_QUANT_GROUPS;   // groups of 4 warps take slabs round-robin
 constexpr int QUANT_WARPS = 4 * QUANT_GROUPS;
 constexpr int NUM_THREADS = (2 + QUANT_WARPS) * 32;
 constexpr int TB_BYTES = SLAB_K * 8;       // {smooth, 1/smooth} of a slab's columns
@@ -73,7 +90,6 @@ struct Params {
   float* lora;            // [M_pad, R]
   void* lora16;           // 16-bit form of lora (fp16 [M_pad, R] or bf16 [2, M_pad, R]) or null
   int M, K, R, M_pad;
-  int dbg;                // TEMP diagnostic switches
 };
 
 template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t v);
@@ -293,14 +309,14 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
       const uint32_t b_addr = a_addr + X_BYTES;
       if (elect_one()) {
-        if (has_lora && !(p.dbg & 64)) {
+        if (has_lora) {
 #pragma unroll
           for (int j = 0; j < SLAB_K / 16; ++j)
             mma_f16<1>(tmem_acc, smem_desc(kDescA, a_addr + j * 32), smem_desc(kDescB, b_addr + j * 2048), kIdesc,
                        (i | j) != 0 ? 1u : 0u);
         }
-        if (has_lora) { if (!(p.dbg & 128)) tc_commit(&empty[s]); if (i == my_slabs - 1) tc_commit(acc_done); }
-        else if (!(p.dbg & 128)) mbar_arrive(&empty[s]);
+        if (has_lora) { tc_commit(&empty[s]); if (i == my_slabs - 1) tc_commit(acc_done); }
+        else mbar_arrive(&empty[s]);
       }
       __syncwarp();
     }
@@ -345,7 +361,6 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[s]);
-      if (p.dbg & 16) continue;
 
       const int k0 = k_begin + i * SLAB_K + g * 16;
       const int gi = k0 >> 4;
@@ -354,7 +369,6 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         const int row = row_base + 8 * rr;
         uint32_t clo, chi, sb;
         quantize_group(f[rr], clo, chi, sb);
-        if ((p.dbg & 32) && clo != 0x12345678u) continue;
         *reinterpret_cast<uint2*>(act_base + static_cast<size_t>(row) * (p.K >> 1) + (k0 >> 1)) = make_uint2(clo, chi);
         p.scales[static_cast<size_t>(gi) * p.M_pad + m0 + row] = static_cast<uint8_t>(sb);
         if (p.scales_swz != nullptr) p.scales_swz[sf_swizzled_offset(m0 + row, gi, groups)] = static_cast<uint8_t>(sb);
@@ -523,7 +537,6 @@ static int launch_qf(const void* x, const void* w, const qf::Params& p, cudaStre
     configured = true;
   }
   int ks = pick_k_split(p.M_pad, p.K);
-  { const char* e = getenv("SVDQ_KS"); if (e) ks = atoi(e); }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.M_pad / qf::TILE_M, ks, 1);
   cfg.blockDim = dim3(qf::NUM_THREADS, 1, 1);
@@ -537,7 +550,7 @@ static int launch_qf(const void* x, const void* w, const qf::Params& p, cudaStre
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  { const char* e = getenv("SVDQ_PDL"); cfg.numAttrs = (e == nullptr || atoi(e) != 0) ? 2 : 1; }
+  cfg.numAttrs = 2;
   if (cudaLaunchKernelEx(&cfg, kern, tmX, tmW, p) != cudaSuccess) return SVDQ_ERR_LAUNCH;
   return SVDQ_OK;
 }
@@ -579,7 +592,6 @@ int launch_quantize_fused(const void* x, const void* lora_down, const void* smoo
   p.lora = lora_act;
   p.lora16 = lora_act16;
   p.M = M; p.K = K; p.R = R; p.M_pad = M_pad;
-  { const char* e = getenv("SVDQ_DEBUG"); p.dbg = e ? atoi(e) : 0; }
   const int rp = R <= 64 ? 64 : (R <= 128 ? 128 : 256);
   if (dtype == SVDQ_DTYPE_F16) {
     if (rp == 64) return launch_qf<__half, 64>(x, lora_down, p, stream);
