@@ -33,6 +33,13 @@ sys.path.insert(0, ROOT)
 
 NSETS = 6  # rotating input/output sets: 6 x ~70 MB is > 3 x the 126 MB L2
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised
+# under profiles/ (one launch each, c1).  Output lines are still in L2 when a captured launch ends, so
+# the write-back of y / act shows up in later launches, not here.
+NCU_DRAM_BYTES = {
+    "c1": {"gemm_w4a4_kernel": 17_996_544, "quantize_fused_kernel": 34_494_208},
+}
+
 
 def _peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -316,12 +323,14 @@ def run_ours(args):
             "quantizer_pct_of_8tbs_nominal": 100.0 * q_gbs / 8000.0,
         },
         "roofline": {"bound": "tensor", "achieved": g_tflops, "peak": nvfp4_peak, "unit": "TFLOP/s",
-                     "frac": g_tflops / nvfp4_peak, "traffic": None,
+                     "frac": g_tflops / nvfp4_peak, "traffic": NCU_DRAM_BYTES.get(shape.name, {}).get("gemm_w4a4_kernel"),
+                     "algorithmic_bytes": M_pad * K // 2 + N * K // 2 + (M_pad + N) * K // 16 + M_pad * N * 2 + (M_pad + N) * R * 2,
                      "kernel": "gemm_w4a4_kernel",
                      "peak_note": f"4 x {peaks['source']} bf16 cuBLAS burst ({peaks['bf16_tflops']} TF/s): no NVFP4 figure is measured on this pool; "
                                   "4 is the nominal nvfp4:bf16 rate ratio"},
         "roofline_quantizer": {"bound": "hbm", "achieved": q_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                               "frac": q_gbs / peaks["hbm_gbs"], "traffic": None, "kernel": "quantize_fused_kernel",
+                               "frac": q_gbs / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES.get(shape.name, {}).get("quantize_fused_kernel"),
+                               "algorithmic_bytes": qbytes, "kernel": "quantize_fused_kernel",
                                "peak_note": f"{peaks['source']} copy bandwidth"},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
                 "ms_per_step": e2e_ms, "steps": e2e_steps, "matches_device_path": bool(same)},
