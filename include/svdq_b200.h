@@ -156,6 +156,18 @@ int svdq_linear_plan_create(svdq_linear_plan** plan, int max_M, int K, int N, in
                             const void* lora_up_host, const void* smooth_host, const void* wcscales_host,
                             const void* bias_host);
 int svdq_linear_plan_forward_host(svdq_linear_plan* plan, const void* x_host, void* y_host, int M);
+/*
+ * Pipelined form of the same call.  svdq_linear_plan_submit queues x copy -> quantizer -> GEMM ->
+ * y copy for one batch and returns; up to two batches are in flight on three streams (copy in,
+ * kernels, copy out), so the PCIe transfers of neighbouring batches overlap the kernels and each
+ * other.  A third submit first waits for the oldest batch.  svdq_linear_plan_wait returns when
+ * every submitted batch has its y on the host.  x_host / y_host of a batch must stay valid (and y
+ * unread) until a wait, or the second-next submit, has returned.  Page-locked buffers are copied
+ * from and to directly; pageable ones pass through staging buffers of the plan.
+ * svdq_linear_plan_forward_host(...) is submit followed by wait.
+ */
+int svdq_linear_plan_submit(svdq_linear_plan* plan, const void* x_host, void* y_host, int M);
+int svdq_linear_plan_wait(svdq_linear_plan* plan);
 void svdq_linear_plan_destroy(svdq_linear_plan* plan);
 
 #ifdef __cplusplus

@@ -33,6 +33,8 @@ SIGNATURES = {
     "svdq_device_status": (c_int, [POINTER(c_uint)]),
     "svdq_linear_plan_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int] + [c_void_p] * 7),
     "svdq_linear_plan_forward_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "svdq_linear_plan_submit": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
+    "svdq_linear_plan_wait": (c_int, [c_void_p]),
     "svdq_linear_plan_destroy": (None, [c_void_p]),
 }
 

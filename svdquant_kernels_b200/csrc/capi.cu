@@ -138,13 +138,28 @@ int svdq_device_status(unsigned int out[4]) {
 // ---------------------------------------------------------------------------
 // host-buffer plan
 // ---------------------------------------------------------------------------
+// Two slots of per-call buffers and three streams (host->device, compute, device->host), so that the
+// copies of neighbouring calls overlap the kernels and each other (PCIe is full duplex).  A slot's
+// life: x copy -> quantizer + GEMM -> y copy; events hand it from stream to stream and keep a slot's
+// next use behind its previous one.
+constexpr int kPlanSlots = 2;
+
+struct PlanSlot {
+  void *x, *act, *ascales, *ascales_swz, *lora_act16, *y;
+  float* lora_act;
+  void *x_pin, *y_pin;                                           // pinned staging for pageable caller buffers
+  cudaEvent_t x_ready, computed, y_done;
+  void* y_user;                                                  // pageable destination still to be filled from y_pin
+  size_t y_bytes;
+  bool busy;
+};
+
 struct svdq_linear_plan {
   int max_M, max_M_pad, K, N, R, dtype;
-  cudaStream_t stream;
-  void *x, *act, *ascales, *ascales_swz, *lora_act16, *y;       // per-call device buffers
-  float* lora_act;
+  cudaStream_t s_in, s_run, s_out;
+  PlanSlot slot[kPlanSlots];
+  unsigned long long submitted;
   void *wgt, *wscales_swz, *lora_down, *lora_up, *smooth, *smooth_table, *wc, *bias;  // resident weights
-  void *x_pin, *y_pin;                                           // pinned staging
 };
 
 static bool is_pinned_host(const void* ptr) {
@@ -173,33 +188,42 @@ int svdq_linear_plan_create(svdq_linear_plan** out, int max_M, int K, int N, int
   if (p == nullptr) return SVDQ_ERR_CUDA;
   p->max_M = max_M; p->max_M_pad = max_M_pad; p->K = K; p->N = N; p->R = R; p->dtype = dtype;
   int rc = SVDQ_OK;
-  bool bad = cudaStreamCreateWithFlags(&p->stream, cudaStreamNonBlocking) != cudaSuccess;
+  bool bad = cudaStreamCreateWithFlags(&p->s_in, cudaStreamNonBlocking) != cudaSuccess;
+  bad = bad || cudaStreamCreateWithFlags(&p->s_run, cudaStreamNonBlocking) != cudaSuccess;
+  bad = bad || cudaStreamCreateWithFlags(&p->s_out, cudaStreamNonBlocking) != cudaSuccess;
   const size_t mp = static_cast<size_t>(max_M_pad);
-  bad = bad || cudaMalloc(&p->x, static_cast<size_t>(max_M) * K * 2) != cudaSuccess;
-  bad = bad || cudaMalloc(&p->act, mp * K / 2) != cudaSuccess;
-  bad = bad || cudaMalloc(&p->ascales, mp * K / 16) != cudaSuccess;
-  bad = bad || cudaMalloc(&p->ascales_swz, mp * K / 16) != cudaSuccess;
-  bad = bad || cudaMalloc(&p->lora_act, mp * (R > 0 ? R : 1) * 4) != cudaSuccess;
-  bad = bad || cudaMalloc(&p->lora_act16, mp * (R > 0 ? R : 1) * 4) != cudaSuccess;   // bf16 keeps two planes
-  bad = bad || cudaMalloc(&p->y, mp * N * 2) != cudaSuccess;
-  bad = bad || cudaMallocHost(&p->x_pin, static_cast<size_t>(max_M) * K * 2) != cudaSuccess;
-  bad = bad || cudaMallocHost(&p->y_pin, mp * N * 2) != cudaSuccess;
+  for (int i = 0; i < kPlanSlots && !bad; ++i) {
+    PlanSlot& q = p->slot[i];
+    bad = bad || cudaMalloc(&q.x, static_cast<size_t>(max_M) * K * 2) != cudaSuccess;
+    bad = bad || cudaMalloc(&q.act, mp * K / 2) != cudaSuccess;
+    bad = bad || cudaMalloc(&q.ascales, mp * K / 16) != cudaSuccess;
+    bad = bad || cudaMalloc(&q.ascales_swz, mp * K / 16) != cudaSuccess;
+    bad = bad || cudaMalloc(&q.lora_act, mp * (R > 0 ? R : 1) * 4) != cudaSuccess;
+    bad = bad || cudaMalloc(&q.lora_act16, mp * (R > 0 ? R : 1) * 4) != cudaSuccess;   // bf16 keeps two planes
+    bad = bad || cudaMalloc(&q.y, mp * N * 2) != cudaSuccess;
+    bad = bad || cudaMallocHost(&q.x_pin, static_cast<size_t>(max_M) * K * 2) != cudaSuccess;
+    bad = bad || cudaMallocHost(&q.y_pin, mp * N * 2) != cudaSuccess;
+    bad = bad || cudaEventCreateWithFlags(&q.x_ready, cudaEventDisableTiming) != cudaSuccess;
+    bad = bad || cudaEventCreateWithFlags(&q.computed, cudaEventDisableTiming) != cudaSuccess;
+    bad = bad || cudaEventCreateWithFlags(&q.y_done, cudaEventDisableTiming) != cudaSuccess;
+  }
   if (bad) rc = SVDQ_ERR_CUDA;
+  cudaStream_t st = p->s_run;
   void* wscales_dev = nullptr;
-  if (rc == SVDQ_OK) rc = dev_upload(&p->wgt, wgt_host, static_cast<size_t>(N) * K / 2, p->stream);
-  if (rc == SVDQ_OK) rc = dev_upload(&wscales_dev, wscales_host, static_cast<size_t>(N) * K / 16, p->stream);
+  if (rc == SVDQ_OK) rc = dev_upload(&p->wgt, wgt_host, static_cast<size_t>(N) * K / 2, st);
+  if (rc == SVDQ_OK) rc = dev_upload(&wscales_dev, wscales_host, static_cast<size_t>(N) * K / 16, st);
   if (rc == SVDQ_OK && cudaMalloc(&p->wscales_swz, static_cast<size_t>(N) * K / 16) != cudaSuccess) rc = SVDQ_ERR_CUDA;
-  if (rc == SVDQ_OK) rc = launch_swizzle_scales(wscales_dev, p->wscales_swz, K / 16, N, p->stream);
-  if (rc == SVDQ_OK) rc = dev_upload(&p->lora_down, lora_down_host, static_cast<size_t>(K) * R * 2, p->stream);
-  if (rc == SVDQ_OK) rc = dev_upload(&p->lora_up, lora_up_host, static_cast<size_t>(N) * R * 2, p->stream);
-  if (rc == SVDQ_OK) rc = dev_upload(&p->smooth, smooth_host, static_cast<size_t>(K) * 2, p->stream);
+  if (rc == SVDQ_OK) rc = launch_swizzle_scales(wscales_dev, p->wscales_swz, K / 16, N, st);
+  if (rc == SVDQ_OK) rc = dev_upload(&p->lora_down, lora_down_host, static_cast<size_t>(K) * R * 2, st);
+  if (rc == SVDQ_OK) rc = dev_upload(&p->lora_up, lora_up_host, static_cast<size_t>(N) * R * 2, st);
+  if (rc == SVDQ_OK) rc = dev_upload(&p->smooth, smooth_host, static_cast<size_t>(K) * 2, st);
   if (rc == SVDQ_OK && p->smooth != nullptr) {
     if (cudaMalloc(&p->smooth_table, static_cast<size_t>(K) * 8 + 16) != cudaSuccess) rc = SVDQ_ERR_CUDA;
-    if (rc == SVDQ_OK) rc = launch_smooth_table(p->smooth, p->smooth_table, K, dtype, p->stream);
+    if (rc == SVDQ_OK) rc = launch_smooth_table(p->smooth, p->smooth_table, K, dtype, st);
   }
-  if (rc == SVDQ_OK) rc = dev_upload(&p->wc, wcscales_host, static_cast<size_t>(N) * 2, p->stream);
-  if (rc == SVDQ_OK) rc = dev_upload(&p->bias, bias_host, static_cast<size_t>(N) * 2, p->stream);
-  if (rc == SVDQ_OK && cudaStreamSynchronize(p->stream) != cudaSuccess) rc = SVDQ_ERR_CUDA;
+  if (rc == SVDQ_OK) rc = dev_upload(&p->wc, wcscales_host, static_cast<size_t>(N) * 2, st);
+  if (rc == SVDQ_OK) rc = dev_upload(&p->bias, bias_host, static_cast<size_t>(N) * 2, st);
+  if (rc == SVDQ_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = SVDQ_ERR_CUDA;
   if (wscales_dev != nullptr) cudaFree(wscales_dev);
   if (rc != SVDQ_OK) {
     svdq_linear_plan_destroy(p);
@@ -209,40 +233,97 @@ int svdq_linear_plan_create(svdq_linear_plan** out, int max_M, int K, int N, int
   return SVDQ_OK;
 }
 
-int svdq_linear_plan_forward_host(svdq_linear_plan* p, const void* x_host, void* y_host, int M) {
+// Finish the call that last used slot `i`: wait for its y copy and, for a pageable y, move the rows
+// out of the staging buffer.
+static int plan_retire(svdq_linear_plan* p, int i) {
+  PlanSlot& q = p->slot[i];
+  if (!q.busy) return SVDQ_OK;
+  q.busy = false;
+  if (cudaEventSynchronize(q.y_done) != cudaSuccess) return SVDQ_ERR_CUDA;
+  if (q.y_user != nullptr) { memcpy(q.y_user, q.y_pin, q.y_bytes); q.y_user = nullptr; }
+  return SVDQ_OK;
+}
+
+int svdq_linear_plan_submit(svdq_linear_plan* p, const void* x_host, void* y_host, int M) {
   if (p == nullptr || x_host == nullptr || y_host == nullptr) return SVDQ_ERR_NULL;
   if (M <= 0 || M > p->max_M) return SVDQ_ERR_SHAPE;
+  const int i = static_cast<int>(p->submitted % kPlanSlots);
+  int rc = plan_retire(p, i);                      // at most kPlanSlots calls are in flight
+  if (rc != SVDQ_OK) return rc;
+  PlanSlot& q = p->slot[i];
   const int M_pad = (M + 255) / 256 * 256;
   const size_t xbytes = static_cast<size_t>(M) * p->K * 2, ybytes = static_cast<size_t>(M) * p->N * 2;
-  // page-locked caller buffers are copied from directly; pageable ones go through the plan's pinned staging
-  const bool x_pinned = is_pinned_host(x_host), y_pinned = is_pinned_host(y_host);
+  // page-locked caller buffers are copied from and to directly; pageable ones go through the slot's staging
   const void* x_src = x_host;
-  if (!x_pinned) { memcpy(p->x_pin, x_host, xbytes); x_src = p->x_pin; }
-  if (cudaMemcpyAsync(p->x, x_src, xbytes, cudaMemcpyHostToDevice, p->stream) != cudaSuccess) return SVDQ_ERR_CUDA;
-  int rc = svdq_quantize_w4a4_act_fuse_lora(p->x, p->lora_down, p->smooth, p->smooth_table, p->act, p->ascales, p->lora_act,
-                                            p->ascales_swz, p->lora_act16, M, p->K, p->R, M_pad, p->dtype,
-                                            SVDQ_QUANT_AUTO, p->stream);
+  if (!is_pinned_host(x_host)) { memcpy(q.x_pin, x_host, xbytes); x_src = q.x_pin; }
+  const bool y_pinned = is_pinned_host(y_host);
+  bool bad = false;
+  // x copy: after the kernels of the slot's previous call have read the old x (stream order on s_run
+  // plus this wait; `computed` of a never-used slot is complete by definition)
+  bad = bad || cudaStreamWaitEvent(p->s_in, q.computed, 0) != cudaSuccess;
+  bad = bad || cudaMemcpyAsync(q.x, x_src, xbytes, cudaMemcpyHostToDevice, p->s_in) != cudaSuccess;
+  bad = bad || cudaEventRecord(q.x_ready, p->s_in) != cudaSuccess;
+  // kernels: after x has landed and the slot's previous y has left the device
+  bad = bad || cudaStreamWaitEvent(p->s_run, q.x_ready, 0) != cudaSuccess;
+  bad = bad || cudaStreamWaitEvent(p->s_run, q.y_done, 0) != cudaSuccess;
+  if (bad) return SVDQ_ERR_CUDA;
+  rc = svdq_quantize_w4a4_act_fuse_lora(q.x, p->lora_down, p->smooth, p->smooth_table, q.act, q.ascales, q.lora_act,
+                                        q.ascales_swz, q.lora_act16, M, p->K, p->R, M_pad, p->dtype, SVDQ_QUANT_AUTO,
+                                        p->s_run);
   if (rc != SVDQ_OK) return rc;
-  rc = svdq_gemm_w4a4(p->act, p->wgt, p->ascales_swz, p->wscales_swz, p->R > 0 ? p->lora_act16 : nullptr,
-                      p->R > 0 ? p->lora_up : nullptr, p->wc, p->bias, p->y, M_pad, p->N, p->K, p->R, p->dtype, 0,
-                      p->stream);
+  rc = svdq_gemm_w4a4(q.act, p->wgt, q.ascales_swz, p->wscales_swz, p->R > 0 ? q.lora_act16 : nullptr,
+                      p->R > 0 ? p->lora_up : nullptr, p->wc, p->bias, q.y, M_pad, p->N, p->K, p->R, p->dtype, 0,
+                      p->s_run);
   if (rc != SVDQ_OK) return rc;
-  void* y_dst = y_pinned ? y_host : p->y_pin;
-  if (cudaMemcpyAsync(y_dst, p->y, ybytes, cudaMemcpyDeviceToHost, p->stream) != cudaSuccess) return SVDQ_ERR_CUDA;
-  if (cudaStreamSynchronize(p->stream) != cudaSuccess) return SVDQ_ERR_CUDA;
-  if (!y_pinned) memcpy(y_host, p->y_pin, ybytes);
+  bad = bad || cudaEventRecord(q.computed, p->s_run) != cudaSuccess;
+  // y copy
+  bad = bad || cudaStreamWaitEvent(p->s_out, q.computed, 0) != cudaSuccess;
+  bad = bad || cudaMemcpyAsync(y_pinned ? y_host : q.y_pin, q.y, ybytes, cudaMemcpyDeviceToHost, p->s_out) != cudaSuccess;
+  bad = bad || cudaEventRecord(q.y_done, p->s_out) != cudaSuccess;
+  if (bad) return SVDQ_ERR_CUDA;
+  q.y_user = y_pinned ? nullptr : y_host;
+  q.y_bytes = ybytes;
+  q.busy = true;
+  ++p->submitted;
   return SVDQ_OK;
+}
+
+int svdq_linear_plan_wait(svdq_linear_plan* p) {
+  if (p == nullptr) return SVDQ_ERR_NULL;
+  // oldest first
+  for (int k = 0; k < kPlanSlots; ++k) {
+    const int rc = plan_retire(p, static_cast<int>((p->submitted + k) % kPlanSlots));
+    if (rc != SVDQ_OK) return rc;
+  }
+  return SVDQ_OK;
+}
+
+int svdq_linear_plan_forward_host(svdq_linear_plan* p, const void* x_host, void* y_host, int M) {
+  const int rc = svdq_linear_plan_submit(p, x_host, y_host, M);
+  return rc != SVDQ_OK ? rc : svdq_linear_plan_wait(p);
 }
 
 void svdq_linear_plan_destroy(svdq_linear_plan* p) {
   if (p == nullptr) return;
-  void* dev[] = {p->x, p->act, p->ascales, p->ascales_swz, p->lora_act, p->lora_act16, p->y, p->wgt,
-                 p->wscales_swz, p->lora_down, p->lora_up, p->smooth, p->smooth_table, p->wc, p->bias};
+  if (p->s_in != nullptr) cudaStreamSynchronize(p->s_in);
+  if (p->s_run != nullptr) cudaStreamSynchronize(p->s_run);
+  if (p->s_out != nullptr) cudaStreamSynchronize(p->s_out);
+  for (PlanSlot& q : p->slot) {
+    void* dev[] = {q.x, q.act, q.ascales, q.ascales_swz, q.lora_act, q.lora_act16, q.y};
+    for (void* d : dev)
+      if (d != nullptr) cudaFree(d);
+    if (q.x_pin != nullptr) cudaFreeHost(q.x_pin);
+    if (q.y_pin != nullptr) cudaFreeHost(q.y_pin);
+    if (q.x_ready != nullptr) cudaEventDestroy(q.x_ready);
+    if (q.computed != nullptr) cudaEventDestroy(q.computed);
+    if (q.y_done != nullptr) cudaEventDestroy(q.y_done);
+  }
+  void* dev[] = {p->wgt, p->wscales_swz, p->lora_down, p->lora_up, p->smooth, p->smooth_table, p->wc, p->bias};
   for (void* d : dev)
     if (d != nullptr) cudaFree(d);
-  if (p->x_pin != nullptr) cudaFreeHost(p->x_pin);
-  if (p->y_pin != nullptr) cudaFreeHost(p->y_pin);
-  if (p->stream != nullptr) cudaStreamDestroy(p->stream);
+  if (p->s_in != nullptr) cudaStreamDestroy(p->s_in);
+  if (p->s_run != nullptr) cudaStreamDestroy(p->s_run);
+  if (p->s_out != nullptr) cudaStreamDestroy(p->s_out);
   delete p;
 }
 

@@ -305,6 +305,26 @@ class LinearPlan:
         _lib.check(rc, "linear_plan_forward_host")
         return y_host
 
+    def submit(self, x_host: torch.Tensor, y_host: torch.Tensor) -> None:
+        """Queue one batch (x copy, kernels, y copy) and return; at most two are in flight.
+
+        Keep both tensors alive and leave `y_host` unread until `wait()` (or the second-next
+        `submit`) has returned."""
+        assert not x_host.is_cuda and not y_host.is_cuda
+        assert x_host.is_contiguous() and y_host.is_contiguous()
+        M = x_host.shape[0]
+        assert x_host.shape == (M, self.K) and y_host.shape == (M, self.N)
+        assert x_host.dtype == self.dtype and y_host.dtype == self.dtype
+        with torch.cuda.device(self.device):
+            rc = self._lib.svdq_linear_plan_submit(self._handle, _ptr(x_host), _ptr(y_host), M)
+        _lib.check(rc, "linear_plan_submit")
+
+    def wait(self) -> None:
+        """Return once every submitted batch has its y on the host."""
+        with torch.cuda.device(self.device):
+            rc = self._lib.svdq_linear_plan_wait(self._handle)
+        _lib.check(rc, "linear_plan_wait")
+
     def close(self) -> None:
         if self._handle:
             self._lib.svdq_linear_plan_destroy(self._handle)
