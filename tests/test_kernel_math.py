@@ -1,0 +1,112 @@
+"""CPU proofs (numpy, exhaustive where the domain is small) of the arithmetic identities the fused
+quantizer relies on to be bit-exact without IEEE divides or compares.  Each test restates in numpy
+what the kernel computes (svdquant_kernels_b200/csrc/quantize_fused.cu) and compares it with the
+definition the oracle uses."""
+import numpy as np
+
+from oracle import nvfp4_oracle as O
+
+f32 = np.float32
+
+
+def _fma(a, b, c):
+    # a*b is exact in float64 for float32 inputs; the sums below stay far inside 53 bits
+    return (a.astype(np.float64) * b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)
+
+
+def test_three_step_quotient_equals_ieee_division_for_11_bit_mantissas():
+    """q0 = x*r; q = fma(fma(-s, q0, x), r, q0) with r = RN(1/s) equals RN(x/s) for every pair of
+    11-bit mantissas (fp16 and, a fortiori, bf16 inputs widened to fp32)."""
+    x = np.arange(1024, 2048, dtype=np.float32)
+    bad = 0
+    for ms in range(1024, 2048):
+        s = np.full_like(x, f32(ms))
+        r = (f32(1.0) / s).astype(np.float32)
+        q0 = (x * r).astype(np.float32)
+        q = _fma(_fma(-s, q0, x), r, q0)
+        bad += int((q != (x / s).astype(np.float32)).sum())
+    assert bad == 0
+
+
+def test_three_step_division_by_six_is_exact_on_sampled_binades():
+    """amax / 6 through the same three steps with RN(1/6), over every mantissa of five binades."""
+    r6 = f32(1.0) / f32(6.0)
+    bad = 0
+    for start in range(0, 1 << 23, 1 << 21):
+        m = np.arange(start, start + (1 << 21), dtype=np.uint32)
+        for ebits in (100, 127, 128, 129, 140):
+            a = ((np.uint32(ebits) << 23) | m).view(np.float32)
+            q0 = (a * r6).astype(np.float32)
+            e = a.astype(np.float64) - 6.0 * q0.astype(np.float64)
+            e32 = e.astype(np.float32)
+            assert (e32.astype(np.float64) == e).all()          # the remainder is exact
+            q = (q0.astype(np.float64) + e32.astype(np.float64) * np.float64(r6)).astype(np.float32)
+            bad += int((q != (a / f32(6.0)).astype(np.float32)).sum())
+    assert bad == 0
+
+
+def test_quotient_compare_equals_product_compare():
+    """RN(a / s) >= b  <=>  a >= s*b for every positive e4m3 scale, every E2M1 bound and the fp32
+    neighbours of the product (s*b is exact: 4 x 3 significant bits)."""
+    bounds = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+    for s in O._E4M3_POS[1:]:
+        for b in bounds:
+            p = f32(s) * f32(b)
+            assert np.float64(p) == np.float64(s) * np.float64(b)
+            cands, lo, hi = [p], p, p
+            for _ in range(4):
+                lo, hi = np.nextafter(lo, f32(0)), np.nextafter(hi, f32(1e30))
+                cands += [lo, hi]
+            a = np.array(cands, dtype=np.float32)
+            assert (((a / f32(s)).astype(np.float32) >= b) == (a >= p)).all(), (s, b)
+
+
+_LEVELS = np.array([0, .5, 1, 1.5, 2, 3, 4, 6], dtype=np.float64)
+
+
+def _rne_e2m1(w):
+    """float -> E2M1 code, round to nearest, ties to the even code, saturating: the documented
+    behaviour of cvt.rn.satfinite.e2m1x2.f32."""
+    out = np.zeros(w.shape, dtype=np.int64)
+    for i, x in np.ndenumerate(w.astype(np.float64)):
+        if x >= 6:
+            out[i] = 7
+            continue
+        hi = int(np.searchsorted(_LEVELS, x, side="right"))
+        lo = hi - 1
+        dl, dh = x - _LEVELS[lo], _LEVELS[hi] - x
+        out[i] = lo if dl < dh else hi if dh < dl else (lo if lo % 2 == 0 else hi)
+    return out
+
+
+def test_hardware_conversion_of_scaled_floor_counts_the_bounds():
+    """With scale = J * 2^E and m = floor(4|v| / 2^E): the E2M1 conversion of
+    RN(m * RN(RN(1/(4J)) * (1 + 2^-20))) equals #{n in {1,3,5,7,10,14,20} : n*J <= m} for every
+    J in 1..15 and every m up to well past saturation, and never lands on a rounding tie (so the
+    tie rule of the conversion does not matter)."""
+    fudge = f32(1.0) + f32(2.0 ** -20)
+    for J in range(1, 16):
+        rj = f32(f32(f32(1.0) / f32(4 * J)) * fudge)
+        m = np.arange(0, 40 * J + 5, dtype=np.float32)
+        w = (m * rj).astype(np.float32)
+        ref = sum((n * J <= m.astype(np.int64)).astype(np.int64) for n in (1, 3, 5, 7, 10, 14, 20))
+        assert (_rne_e2m1(w) == ref).all(), J
+        ties = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0])
+        assert not np.isin(w.astype(np.float64), ties).any(), J
+
+
+def test_floor_by_rounded_add_and_fused_rescale():
+    """(2^23 + m) * rj - 2^23 * rj evaluated with one rounding is RN(m * rj): 2^23 * rj is exact, so
+    the fused form used by the kernel equals the two-step form the proof above is about."""
+    rng = np.random.default_rng(1)
+    t = (rng.random(200000) * 400).astype(np.float32)
+    a = (t.astype(np.float64) + 8388608.0)
+    a = np.floor(a).astype(np.float32)                      # add of 2^23 rounded toward zero, t >= 0
+    m = (a - f32(8388608.0)).astype(np.float32)
+    assert (m == np.floor(t)).all()
+    for J in (1, 3, 7, 15):
+        rj = f32(f32(f32(1.0) / f32(4 * J)) * (f32(1.0) + f32(2.0 ** -20)))
+        c2 = f32(-8388608.0) * rj
+        assert np.float64(c2) == -8388608.0 * np.float64(rj)
+        fused = (a.astype(np.float64) * np.float64(rj) + np.float64(c2)).astype(np.float32)
+        assert (fused == (m * rj).astype(np.float32)).all()
