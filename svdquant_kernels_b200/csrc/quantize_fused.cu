@@ -171,7 +171,7 @@ __device__ __forceinline__ void quantize_group(float (&f)[16],
   if (sb != 0u && sb != 0x7Eu) {
     // Main path.  scale = J * 2^E with J in 1..15, so with t = 4 |v| / 2^E (an exact power-of-two
     // scaling) the code is the number of n in {1,3,5,7,10,14,20} with n J <= t, i.e. with
-    // n J <= m = floor(t).  m comes from an add of 2^23 rounded toward zero.  m / (4 J) then lies
+    // n J <= m = floor(t).  m / (4 J) then lies
     // on a bound n/4 exactly when m = n J and is at least 1/(4 J) away from every bound otherwise,
     // so m * RN(1/(4 J)) * (1 + 2^-20) is strictly above the bound in the first case and on the
     // right side of it in the second, and the hardware's float -> E2M1 conversion (round to
@@ -181,20 +181,15 @@ __device__ __forceinline__ void quantize_group(float (&f)[16],
     const uint32_t J = e ? 8u + m3 : m3;
     const float mult = __uint_as_float((e ? 139u - e : 138u) << 23);      // 2^(2 - E)
     const float rj = __fmul_rn(__frcp_rn(static_cast<float>(4u * J)), 1.00000095367431640625f);
-    const float c2 = -8388608.0f * rj;             // exact
     uint32_t b[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      float w[2];
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const float v = f[2 * j + h];
-        // (2^23 + m) * rj - 2^23 * rj in one fused operation is RN(m * rj); the sign bit of v rides along
-        // (v is never -0 here: inputs were made +0 and quotients cannot underflow in this path)
-        const float a = __fadd_rz(fabsf(v) * mult, 8388608.0f);
-        w[h] = __uint_as_float(__float_as_uint(fmaf(a, rj, c2)) | (__float_as_uint(v) & 0x80000000u));
-      }
-      b[j] = cvt_e2m1x2(w[1], w[0]);     // low nibble = even element
+      // m = trunc(4 v / 2^E) keeps the sign of v (also as -0 for a small negative v, whose code is
+      // "negative zero" in the reference too; v itself is never -0 here: inputs were made +0 and
+      // quotients cannot underflow in this path)
+      const float w0 = __fmul_rn(truncf(f[2 * j] * mult), rj);
+      const float w1 = __fmul_rn(truncf(f[2 * j + 1] * mult), rj);
+      b[j] = cvt_e2m1x2(w1, w0);     // low nibble = even element
     }
     lo = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
     hi = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);

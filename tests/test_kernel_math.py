@@ -95,18 +95,15 @@ def test_hardware_conversion_of_scaled_floor_counts_the_bounds():
         assert not np.isin(w.astype(np.float64), ties).any(), J
 
 
-def test_floor_by_rounded_add_and_fused_rescale():
-    """(2^23 + m) * rj - 2^23 * rj evaluated with one rounding is RN(m * rj): 2^23 * rj is exact, so
-    the fused form used by the kernel equals the two-step form the proof above is about."""
+def test_signed_truncation_carries_the_sign_through_the_rescale():
+    """The kernel forms trunc(4 v / 2^E) * rj with the sign of v riding along: for negative v this is
+    minus the value for |v| (rounding to nearest is symmetric), and a small negative v gives -0, the
+    'negative zero' code the reference produces for it."""
     rng = np.random.default_rng(1)
     t = (rng.random(200000) * 400).astype(np.float32)
-    a = (t.astype(np.float64) + 8388608.0)
-    a = np.floor(a).astype(np.float32)                      # add of 2^23 rounded toward zero, t >= 0
-    m = (a - f32(8388608.0)).astype(np.float32)
-    assert (m == np.floor(t)).all()
     for J in (1, 3, 7, 15):
         rj = f32(f32(f32(1.0) / f32(4 * J)) * (f32(1.0) + f32(2.0 ** -20)))
-        c2 = f32(-8388608.0) * rj
-        assert np.float64(c2) == -8388608.0 * np.float64(rj)
-        fused = (a.astype(np.float64) * np.float64(rj) + np.float64(c2)).astype(np.float32)
-        assert (fused == (m * rj).astype(np.float32)).all()
+        pos = (np.trunc(t) * rj).astype(np.float32)
+        neg = (np.trunc(-t) * rj).astype(np.float32)
+        assert (neg == -pos).all()
+        assert np.signbit(neg[t < 1]).all() and (neg[t < 1] == 0).all()
