@@ -71,10 +71,12 @@ int svdq_prepare_smooth(const void* smooth, void* smooth_table, int K, int dtype
  *   lora_act   [M_pad, R]    f32  rows >= M are zero
  *   ascales_swz  optional, M_pad*K/16 bytes: the same scales in the 128-row x 4-group
  *                atom order the tensor core reads (needs M_pad % 128 == 0, K % 64 == 0)
- *   lora_act16   optional: lora_act in the 16-bit form svdq_gemm_w4a4 consumes (same format as
- *                lora_up).  dtype f16: [M_pad, R] fp16, rounded once, magnitudes beyond 65504
- *                clamped.  dtype bf16: [2, M_pad, R] bf16 = hi plane then lo plane with
- *                hi = bf16(v), lo = bf16(v - hi)
+ *   lora_act16   optional: lora_act in the 16-bit form svdq_gemm_w4a4 consumes;
+ *                svdq_lora_act16_elems(M_pad, R, dtype) 16-bit elements.  dtype f16: [M_pad, R]
+ *                fp16, rounded once, magnitudes beyond 65504 clamped.  dtype bf16: three
+ *                [M_pad, R] planes - hi = bf16(v), lo = bf16(v - hi), and v as fp16 (clamped) -
+ *                followed by one 32-bit word per 32 rows that is non-zero when some value of
+ *                those rows does not fit fp16
  *   M_pad      rows of the outputs, >= M (the reference pads M up to a multiple of 256)
  * Rows M..M_pad-1 of act / ascales are written as zero bytes, as the oracle does.
  */
@@ -108,10 +110,19 @@ int svdq_quantize_nvfp4_rows(const void* x, void* codes, void* scales, void* sca
  */
 int svdq_swizzle_scales(const void* scales, void* scales_swz, int k_groups, int rows, void* stream);
 
-/* f32 lora_act (count = M * R values) -> its 16-bit form of type dtype, as described for lora_act16
- * above; dst holds count values for f16, 2 * count for bf16 (stands in for the cast launch_v2 does
- * at cute_kernels/gemm_w4a4/kernel_v2_fa4.py:176-184). */
-int svdq_cast_lora_act(const float* src, void* dst, long long count, int dtype, void* stream);
+/* 16-bit elements of the lora_act16 form of a [rows, R] lora_act for dtype (-1 on bad arguments). */
+long long svdq_lora_act16_elems(int rows, int R, int dtype);
+
+/* f32 lora_act [rows, R] -> its 16-bit form of type dtype, as described for lora_act16 above (stands
+ * in for the cast launch_v2 does at cute_kernels/gemm_w4a4/kernel_v2_fa4.py:176-184).  For bf16 this
+ * route marks every row block "does not fit fp16" without looking, so the GEMM takes two passes. */
+int svdq_cast_lora_act(const float* src, void* dst, int rows, int R, int dtype, void* stream);
+
+/* HOST helper: bf16 lora_up [count values] -> fp16, for svdq_gemm_w4a4's lora_up_f16.  Returns
+ * SVDQ_ERR_UNSUPPORTED (and an unusable output) if a value is NaN or beyond fp16's range; values
+ * below 2^-14 lose bits, as they would in any fp16 LoRA.  No counterpart in the reference, which
+ * multiplies bf16 lora_act by bf16 lora_up in one pass and accepts the 7e-3 error of that. */
+int svdq_lora_up_to_f16(const void* lora_up_bf16_host, void* out_f16_host, long long count);
 
 /*
  * W4A4 GEMM + LoRA-up + per-column affine.
@@ -122,6 +133,9 @@ int svdq_cast_lora_act(const float* src, void* dst, long long count, int dtype, 
  *   ascales_swz  M*K/16 bytes      wscales_swz N*K/16 bytes   (atom order, see above)
  *   lora_act16  16-bit form of lora_act for dtype (see above) or NULL
  *   lora_up     [N, R] of type dtype or NULL (both or neither)
+ *   lora_up_f16 dtype bf16 only, optional: lora_up as fp16 [N, R] on the device.  With it, output
+ *               tiles whose rows of lora_act all fit fp16 (the words behind lora_act16) take one
+ *               fp16 LoRA pass instead of the hi + lo bf16 passes; other tiles are unaffected.
  *   wcscales    [N] or NULL        bias       [N] or NULL     (type = dtype)
  *   y           [M, N] dtype
  * Contract: M % 128 == 0, N % 128 == 0, K % 64 == 0, R % 16 == 0 (svdq_gemm_w4a4_supported).
@@ -130,7 +144,7 @@ int svdq_cast_lora_act(const float* src, void* dst, long long count, int dtype, 
  *   y = cast( (deq(act) deq(wgt)^T + lora_act16 lora_up^T) * wcscales + bias )
  */
 int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
-                   const void* lora_act16, const void* lora_up, const void* wcscales, const void* bias,
+                   const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales, const void* bias,
                    void* y, int M, int N, int K, int R, int dtype, int variant, void* stream);
 
 /* 1 if (M, N, K, R) is inside the GEMM contract, else 0. */

@@ -27,8 +27,10 @@ SIGNATURES = {
     "svdq_quantizer_max_active_clusters": (c_int, [c_int, c_int, c_int]),
     "svdq_quantize_nvfp4_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "svdq_swizzle_scales": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
-    "svdq_cast_lora_act": (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_void_p]),
-    "svdq_gemm_w4a4": (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_void_p]),
+    "svdq_lora_act16_elems": (c_longlong, [c_int, c_int, c_int]),
+    "svdq_cast_lora_act": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "svdq_lora_up_to_f16": (c_int, [c_void_p, c_void_p, c_longlong]),
+    "svdq_gemm_w4a4": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p]),
     "svdq_gemm_w4a4_supported": (c_int, [c_int, c_int, c_int, c_int]),
     "svdq_device_status": (c_int, [POINTER(c_uint)]),
     "svdq_linear_plan_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int] + [c_void_p] * 7),

@@ -4,6 +4,11 @@
 #include <cstring>
 #include <new>
 
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <vector>
+
+#include "nvfp4_math.cuh"
 #include "sm100.cuh"
 #include "svdq_internal.h"
 
@@ -96,11 +101,32 @@ int svdq_swizzle_scales(const void* scales, void* scales_swz, int k_groups, int 
   return launch_swizzle_scales(scales, scales_swz, k_groups, rows, static_cast<cudaStream_t>(stream));
 }
 
-int svdq_cast_lora_act(const float* src, void* dst, long long count, int dtype, void* stream) {
-  if (count < 0) return SVDQ_ERR_SHAPE;
-  if (count == 0) return SVDQ_OK;
+long long svdq_lora_act16_elems(int rows, int R, int dtype) {
+  if (rows < 0 || R < 0 || (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16)) return -1;
+  return static_cast<long long>(lora16_elems(static_cast<size_t>(rows), static_cast<size_t>(R), dtype == SVDQ_DTYPE_BF16));
+}
+
+int svdq_cast_lora_act(const float* src, void* dst, int rows, int R, int dtype, void* stream) {
+  if (rows < 0 || R < 0) return SVDQ_ERR_SHAPE;
+  if (rows == 0 || R == 0) return SVDQ_OK;
   if (src == nullptr || dst == nullptr) return SVDQ_ERR_NULL;
-  return launch_cast_f32(src, dst, count, dtype, static_cast<cudaStream_t>(stream));
+  if (!aligned16(dst)) return SVDQ_ERR_ALIGN;
+  return launch_cast_f32(src, dst, rows, R, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int svdq_lora_up_to_f16(const void* lora_up_bf16_host, void* out_f16_host, long long count) {
+  if (count < 0) return SVDQ_ERR_SHAPE;
+  if (count > 0 && (lora_up_bf16_host == nullptr || out_f16_host == nullptr)) return SVDQ_ERR_NULL;
+  const uint16_t* src = static_cast<const uint16_t*>(lora_up_bf16_host);
+  __half* dst = static_cast<__half*>(out_f16_host);
+  for (long long i = 0; i < count; ++i) {
+    const uint32_t bits = static_cast<uint32_t>(src[i]) << 16;
+    float v;
+    memcpy(&v, &bits, 4);
+    if (!(v >= -65504.0f && v <= 65504.0f)) return SVDQ_ERR_UNSUPPORTED;     // out of fp16 range or NaN: no copy
+    dst[i] = __float2half_rn(v);
+  }
+  return SVDQ_OK;
 }
 
 int svdq_quantizer_max_active_clusters(int R, int k_split, int dtype) {
@@ -111,8 +137,8 @@ int svdq_quantizer_max_active_clusters(int R, int k_split, int dtype) {
 int svdq_gemm_w4a4_supported(int M, int N, int K, int R) { return gemm_supported(M, N, K, R) ? 1 : 0; }
 
 int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
-                   const void* lora_act16, const void* lora_up, const void* wcscales, const void* bias, void* y, int M,
-                   int N, int K, int R, int dtype, int variant, void* stream) {
+                   const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
+                   const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant, void* stream) {
   if (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16) return SVDQ_ERR_DTYPE;
   if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
   if (act == nullptr || wgt == nullptr || ascales_swz == nullptr || wscales_swz == nullptr || y == nullptr)
@@ -121,10 +147,10 @@ int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, co
   if (R > 0 && lora_act16 == nullptr) return SVDQ_ERR_NULL;
   if (lora_act16 == nullptr) R = 0;
   if (!aligned16(act) || !aligned16(wgt) || !aligned16(ascales_swz) || !aligned16(wscales_swz) ||
-      !aligned16(lora_act16) || !aligned16(lora_up) || !aligned16(y))
+      !aligned16(lora_act16) || !aligned16(lora_up) || !aligned16(lora_up_f16) || !aligned16(y))
     return SVDQ_ERR_ALIGN;
-  return launch_gemm_w4a4(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, wcscales, bias, y, M, N, K, R, dtype,
-                          variant, static_cast<cudaStream_t>(stream));
+  return launch_gemm_w4a4(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N,
+                          K, R, dtype, variant, static_cast<cudaStream_t>(stream));
 }
 
 int svdq_device_status(unsigned int out[4]) {
@@ -159,7 +185,7 @@ struct svdq_linear_plan {
   cudaStream_t s_in, s_run, s_out;
   PlanSlot slot[kPlanSlots];
   unsigned long long submitted;
-  void *wgt, *wscales_swz, *lora_down, *lora_up, *smooth, *smooth_table, *wc, *bias;  // resident weights
+  void *wgt, *wscales_swz, *lora_down, *lora_up, *lora_up_f16, *smooth, *smooth_table, *wc, *bias;  // resident weights
 };
 
 static bool is_pinned_host(const void* ptr) {
@@ -199,7 +225,7 @@ int svdq_linear_plan_create(svdq_linear_plan** out, int max_M, int K, int N, int
     bad = bad || cudaMalloc(&q.ascales, mp * K / 16) != cudaSuccess;
     bad = bad || cudaMalloc(&q.ascales_swz, mp * K / 16) != cudaSuccess;
     bad = bad || cudaMalloc(&q.lora_act, mp * (R > 0 ? R : 1) * 4) != cudaSuccess;
-    bad = bad || cudaMalloc(&q.lora_act16, mp * (R > 0 ? R : 1) * 4) != cudaSuccess;   // bf16 keeps two planes
+    bad = bad || cudaMalloc(&q.lora_act16, 2 * lora16_elems(mp, R > 0 ? R : 1, dtype == SVDQ_DTYPE_BF16) + 16) != cudaSuccess;
     bad = bad || cudaMalloc(&q.y, mp * N * 2) != cudaSuccess;
     bad = bad || cudaMallocHost(&q.x_pin, static_cast<size_t>(max_M) * K * 2) != cudaSuccess;
     bad = bad || cudaMallocHost(&q.y_pin, mp * N * 2) != cudaSuccess;
@@ -216,6 +242,13 @@ int svdq_linear_plan_create(svdq_linear_plan** out, int max_M, int K, int N, int
   if (rc == SVDQ_OK) rc = launch_swizzle_scales(wscales_dev, p->wscales_swz, K / 16, N, st);
   if (rc == SVDQ_OK) rc = dev_upload(&p->lora_down, lora_down_host, static_cast<size_t>(K) * R * 2, st);
   if (rc == SVDQ_OK) rc = dev_upload(&p->lora_up, lora_up_host, static_cast<size_t>(N) * R * 2, st);
+  std::vector<uint16_t> lu16;                      // must outlive the asynchronous upload below
+  if (rc == SVDQ_OK && dtype == SVDQ_DTYPE_BF16 && R > 0) {
+    // fp16 copy of a bf16 lora_up for the single-pass LoRA route (skipped if a value does not fit)
+    lu16.resize(static_cast<size_t>(N) * R);
+    if (svdq_lora_up_to_f16(lora_up_host, lu16.data(), static_cast<long long>(lu16.size())) == SVDQ_OK)
+      rc = dev_upload(&p->lora_up_f16, lu16.data(), lu16.size() * 2, st);
+  }
   if (rc == SVDQ_OK) rc = dev_upload(&p->smooth, smooth_host, static_cast<size_t>(K) * 2, st);
   if (rc == SVDQ_OK && p->smooth != nullptr) {
     if (cudaMalloc(&p->smooth_table, static_cast<size_t>(K) * 8 + 16) != cudaSuccess) rc = SVDQ_ERR_CUDA;
@@ -272,7 +305,8 @@ int svdq_linear_plan_submit(svdq_linear_plan* p, const void* x_host, void* y_hos
                                         p->s_run);
   if (rc != SVDQ_OK) return rc;
   rc = svdq_gemm_w4a4(q.act, p->wgt, q.ascales_swz, p->wscales_swz, p->R > 0 ? q.lora_act16 : nullptr,
-                      p->R > 0 ? p->lora_up : nullptr, p->wc, p->bias, q.y, M_pad, p->N, p->K, p->R, p->dtype, 0,
+                      p->R > 0 ? p->lora_up : nullptr, p->R > 0 ? p->lora_up_f16 : nullptr, p->wc, p->bias, q.y, M_pad, p->N,
+                      p->K, p->R, p->dtype, 0,
                       p->s_run);
   if (rc != SVDQ_OK) return rc;
   bad = bad || cudaEventRecord(q.computed, p->s_run) != cudaSuccess;
@@ -318,7 +352,7 @@ void svdq_linear_plan_destroy(svdq_linear_plan* p) {
     if (q.computed != nullptr) cudaEventDestroy(q.computed);
     if (q.y_done != nullptr) cudaEventDestroy(q.y_done);
   }
-  void* dev[] = {p->wgt, p->wscales_swz, p->lora_down, p->lora_up, p->smooth, p->smooth_table, p->wc, p->bias};
+  void* dev[] = {p->wgt, p->wscales_swz, p->lora_down, p->lora_up, p->lora_up_f16, p->smooth, p->smooth_table, p->wc, p->bias};
   for (void* d : dev)
     if (d != nullptr) cudaFree(d);
   if (p->s_in != nullptr) cudaStreamDestroy(p->s_in);

@@ -43,6 +43,7 @@
 // fp16 as one rounded copy, bf16 as a hi + lo pair (lora_act = hi + lo to 16
 // significant bits) that takes two passes over the same lora_up slab - a single
 // bf16 copy would put the LoRA term's 2^-9 rounding error above the 1e-3 bound.
+#include "nvfp4_math.cuh"
 #include "sm100.cuh"
 #include "svdq_internal.h"
 
@@ -97,6 +98,7 @@ struct Cfg {
 struct Params {
   const void* wc;       // [N] or null
   const void* bias;     // [N] or null
+  const uint32_t* la_flags;   // bf16 only: per 32 rows of lora_act, non-zero = does not fit fp16; null = always two-pass
   int M, N, K, R;
   int tiles_m, tiles_n; // in units of (CG*128) x BN
 };
@@ -130,7 +132,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmLA, const __grid_constant__ CUtensorMap tmLU,
                  const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmSFA,
-                 const __grid_constant__ CUtensorMap tmSFB, const Params p) {
+                 const __grid_constant__ CUtensorMap tmSFB, const __grid_constant__ CUtensorMap tmLAf,
+                 const __grid_constant__ CUtensorMap tmLUf, const Params p) {
   using C = Cfg<CG, BN>;
   constexpr bool kBf16 = std::is_same<OutT, __nv_bfloat16>::value;
 
@@ -176,6 +179,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmY);
     tma_prefetch_desc(&tmSFA); tma_prefetch_desc(&tmSFB);
     if (p.R > 0) { tma_prefetch_desc(&tmLA); tma_prefetch_desc(&tmLU); }
+    if (p.R > 0 && p.la_flags != nullptr) { tma_prefetch_desc(&tmLAf); tma_prefetch_desc(&tmLUf); }
   }
   if (warp == EPI_WARPS + 1) {
     if constexpr (CG == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
@@ -193,10 +197,18 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_sf = tmem_base + C::ACC_STAGES * BN;       // SF_BUFS buffers of [SFA 16 | SFB] columns
 
   const int kt_main = (p.K + BK - 1) / BK;   // the last slab may hold fewer than four 64-element k-blocks
-  constexpr int kLoraParts = kBf16 ? 2 : 1;        // bf16: hi and lo halves of lora_act
   const int lora_slabs = (p.R + 63) / 64;
-  const int kt_lora = kLoraParts * lora_slabs;
-  const int kt_all = kt_main + kt_lora;
+  // bf16 output: lora_act comes as hi and lo bf16 planes (two passes over the same lora_up slab) and
+  // as an fp16 plane; a tile whose 32-row blocks all carry a zero "does not fit fp16" word takes
+  // the fp16 plane and the fp16 copy of lora_up in a single pass.  Every role of both CTAs
+  // evaluates this per tile from the same words, so they agree on the number of slabs.
+  auto lora_fp16 = [&](int mb) -> bool {
+    if (!kBf16 || p.R == 0 || p.la_flags == nullptr) return false;
+    constexpr int kWords = CG * BM / 32;
+    const uint32_t w = lane < kWords ? __ldg(p.la_flags + mb * kWords + lane) : 0u;
+    return __all_sync(0xffffffffu, w == 0u) != 0;
+  };
+  auto lora_parts = [&](bool fp16_pass) -> int { return (kBf16 && !fp16_pass) ? 2 : 1; };
   const int total_tiles = p.tiles_m * p.tiles_n;
   const int k_groups4 = p.K / 64;            // scale atoms along K
 
@@ -209,6 +221,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int m0 = (mb * CG + rank) * BM;
       const int n0 = nb * BN;
       const int nrow0 = n0 + rank * C::B_ROWS;
+      const bool la_fp16 = lora_fp16(mb);
+      const int kt_all = kt_main + lora_parts(la_fp16) * lora_slabs;
       for (int kt = 0; kt < kt_all; ++kt, ++it) {
         const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
         if (!uwait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, it)) { ok = false; break; }
@@ -233,8 +247,13 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {
             const int lt = kt - kt_main;
             const int part = lt / lora_slabs, r0 = (lt % lora_slabs) * 64;
-            tma_load_2d_bar<CG>(st, &tmLA, r0, part * p.M + m0, bar);      // lora_act parts are stacked along rows
-            tma_load_2d_bar<CG>(st + A_BYTES, &tmLU, r0, nrow0, bar);
+            if (la_fp16) {
+              tma_load_2d_bar<CG>(st, &tmLAf, r0, m0, bar);
+              tma_load_2d_bar<CG>(st + A_BYTES, &tmLUf, r0, nrow0, bar);
+            } else {
+              tma_load_2d_bar<CG>(st, &tmLA, r0, part * p.M + m0, bar);    // lora_act parts are stacked along rows
+              tma_load_2d_bar<CG>(st + A_BYTES, &tmLU, r0, nrow0, bar);
+            }
           }
         }
         __syncwarp();
@@ -246,6 +265,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint64_t kDescAB = smem_desc_base(0, 1024, kSwizzle128B);   // K-major, 8-row groups 1024 B apart
       constexpr uint32_t kIdescMain = idesc_nvfp4(BM * CG, BN);
       constexpr uint32_t kIdescLora = idesc_f16(kBf16, kBf16, BM * CG, BN, false, false);
+      constexpr uint32_t kIdescLoraF16 = idesc_f16(false, false, BM * CG, BN, false, false);
       constexpr uint16_t kMask = (CG == 2) ? 3 : 1;
       uint32_t it = 0, tcount = 0, sf_it = 0;
       bool ok = true;
@@ -254,6 +274,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!uwait(&acc_empty[as], aph ^ 1, ctx, kDevWaitAccFree, tcount)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + as * BN;
+        const bool la_fp16 = lora_fp16(tile % p.tiles_m);
+        const int kt_all = kt_main + lora_parts(la_fp16) * lora_slabs;
+        const uint32_t idesc_lora = la_fp16 ? kIdescLoraF16 : kIdescLora;
         for (int kt = 0; kt < kt_all; ++kt, ++it) {
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
           if (!uwait(&full[s], ph, ctx, kDevWaitFull, it)) { ok = false; break; }
@@ -280,7 +303,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 4; ++j)
                 if (j < nkb)
                   mma_f16<CG>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
-                              kIdescLora, (kt | j) != 0 ? 1u : 0u);
+                              idesc_lora, (kt | j) != 0 ? 1u : 0u);
             }
             tc_commit_mask<CG>(&empty[s], kMask);          // stage reusable (in both CTAs) once these MMAs have read it
             if (kt == kt_all - 1) tc_commit_mask<CG>(&acc_full[as], kMask);   // accumulator complete
@@ -299,6 +322,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0, sf_it = 0;
       bool ok = true;
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+        const int kt_all = kt_main + lora_parts(lora_fp16(tile % p.tiles_m)) * lora_slabs;
         for (int kt = 0; kt < kt_all; ++kt, ++it) {
           // Every slab's barrier is waited on in order, LoRA slabs (which carry no scales) included: a
           // waiter that skipped ahead could get two ring revolutions in front of the producer, where the
@@ -445,10 +469,11 @@ bool gemm_supported(int M, int N, int K, int R) {
 
 template <int CG, int BN, typename OutT>
 static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, const void* sfb, const void* la,
-                         const void* lu, const void* wc, const void* bias, void* y, int M, int N, int K, int R,
-                         cudaStream_t stream) {
+                         const void* lu, const void* lu_f16, const void* wc, const void* bias, void* y, int M, int N,
+                         int K, int R, cudaStream_t stream) {
   using C = gemm::Cfg<CG, BN>;
-  CUtensorMap tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB;
+  constexpr bool kBf16 = std::is_same<OutT, __nv_bfloat16>::value;
+  CUtensorMap tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, tmLAf, tmLUf;
   int rc;
   const uint64_t atoms_k = K / 64;
   if ((rc = make_tmap_2d(&tmSFA, sfa, 4, (M / 128) * atoms_k, 128, 512, 4, 128, kTmapSwizzleNone)) != SVDQ_OK) return rc;
@@ -464,6 +489,16 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
     tmLA = tmA; tmLU = tmB;
   }
   gemm::Params p;
+  p.la_flags = nullptr;
+  tmLAf = tmLA; tmLUf = tmLU;
+  if (kBf16 && R > 0 && lu_f16 != nullptr) {
+    // bf16 form of lora_act: planes hi, lo, fp16, then the per-32-row flag words
+    const size_t plane = static_cast<size_t>(M) * R;
+    const void* la_f16 = static_cast<const uint16_t*>(la) + 2 * plane;
+    if ((rc = make_tmap_2d(&tmLAf, la_f16, 2, M, R, static_cast<uint64_t>(R) * 2, gemm::BM, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
+    if ((rc = make_tmap_2d(&tmLUf, lu_f16, 2, N, R, static_cast<uint64_t>(R) * 2, C::B_ROWS, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
+    p.la_flags = lora16_flags(la, plane);
+  }
   p.wc = wc; p.bias = bias;
   p.M = M; p.N = N; p.K = K; p.R = R;
   p.tiles_m = M / (gemm::BM * CG); p.tiles_n = N / BN;
@@ -488,24 +523,25 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, p) != cudaSuccess) return SVDQ_ERR_LAUNCH;
+  if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, tmLAf, tmLUf, p) != cudaSuccess) return SVDQ_ERR_LAUNCH;
   return SVDQ_OK;
 }
 
 template <typename OutT>
 static int launch_gemm_dt(int cg, int bn, const void* act, const void* wgt, const void* sfa, const void* sfb,
-                          const void* la, const void* lu, const void* wc, const void* bias, void* y, int M, int N, int K,
-                          int R, cudaStream_t stream) {
-  if (cg == 2 && bn == 256) return launch_gemm_t<2, 256, OutT>(act, wgt, sfa, sfb, la, lu, wc, bias, y, M, N, K, R, stream);
-  if (cg == 2 && bn == 128) return launch_gemm_t<2, 128, OutT>(act, wgt, sfa, sfb, la, lu, wc, bias, y, M, N, K, R, stream);
-  if (cg == 1 && bn == 256) return launch_gemm_t<1, 256, OutT>(act, wgt, sfa, sfb, la, lu, wc, bias, y, M, N, K, R, stream);
-  return launch_gemm_t<1, 128, OutT>(act, wgt, sfa, sfb, la, lu, wc, bias, y, M, N, K, R, stream);
+                          const void* la, const void* lu, const void* lu_f16, const void* wc, const void* bias, void* y,
+                          int M, int N, int K, int R, cudaStream_t stream) {
+  if (cg == 2 && bn == 256) return launch_gemm_t<2, 256, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, stream);
+  if (cg == 2 && bn == 128) return launch_gemm_t<2, 128, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, stream);
+  if (cg == 1 && bn == 256) return launch_gemm_t<1, 256, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, stream);
+  return launch_gemm_t<1, 128, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, stream);
 }
 
 // variant: 0 = choose; 128 / 256 = one CTA per tile with that N tile; 2128 / 2256 = CTA pairs (256-row tiles)
 int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
-                     const void* lora_act16, const void* lora_up, const void* wcscales, const void* bias, void* y,
-                     int M, int N, int K, int R, int dtype, int variant, cudaStream_t stream) {
+                     const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
+                     const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant,
+                     cudaStream_t stream) {
   if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
   int cg, bn;
   if (variant == 0) {
@@ -519,9 +555,9 @@ int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, 
   if ((cg != 1 && cg != 2) || (bn != 128 && bn != 256)) return SVDQ_ERR_UNSUPPORTED;
   if (M % (128 * cg) != 0 || N % bn != 0) return SVDQ_ERR_SHAPE;
   if (dtype == SVDQ_DTYPE_F16)
-    return launch_gemm_dt<__half>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, wcscales, bias, y, M, N, K, R, stream);
+    return launch_gemm_dt<__half>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, nullptr, wcscales, bias, y, M, N, K, R, stream);
   if (dtype == SVDQ_DTYPE_BF16)
-    return launch_gemm_dt<__nv_bfloat16>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, wcscales, bias, y, M, N, K, R, stream);
+    return launch_gemm_dt<__nv_bfloat16>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R, stream);
   return SVDQ_ERR_DTYPE;
 }
 

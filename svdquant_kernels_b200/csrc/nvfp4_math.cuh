@@ -73,7 +73,11 @@ __device__ __forceinline__ uint32_t e2m1_code(float v, const GroupBounds& g) {
 // lora_act in the 16-bit form the GEMM's dense MMA consumes (same format as lora_up):
 //   fp16: one copy, round to nearest even, magnitudes beyond 65504 clamp to it
 //   bf16: hi = bf16(v) and lo = bf16(v - hi), stored as two [rows, R] planes; hi + lo carries
-//         16 significant bits of v with bf16's full exponent range
+//         16 significant bits of v with bf16's full exponent range.  A third plane holds v as
+//         fp16 (clamped like the fp16 form): where a whole row block is known to fit fp16 the
+//         GEMM multiplies that plane with an fp16 copy of lora_up in one pass instead of two.
+//         Behind the planes: one 32-bit word per 32 rows, non-zero if some value of those rows
+//         does not fit (see lora16_flags)
 __device__ __forceinline__ __half f32_to_f16_sat(float v) {
   return __float2half_rn(fminf(fmaxf(v, -65504.0f), 65504.0f));
 }
@@ -94,6 +98,7 @@ __device__ __forceinline__ void store_lora16<__nv_bfloat16>(void* base, size_t i
   f32_to_bf16_hi_lo(v, hi, lo);
   static_cast<__nv_bfloat16*>(base)[idx] = hi;
   static_cast<__nv_bfloat16*>(base)[plane + idx] = lo;
+  reinterpret_cast<__half*>(base)[2 * plane + idx] = f32_to_f16_sat(v);
 }
 // four consecutive elements at once (idx % 4 == 0)
 template <typename T>
@@ -113,6 +118,22 @@ __device__ __forceinline__ void store_lora16x4<__nv_bfloat16>(void* base, size_t
   __nv_bfloat16* p = static_cast<__nv_bfloat16*>(base);
   *reinterpret_cast<uint2*>(p + idx) = make_uint2(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1));
   *reinterpret_cast<uint2*>(p + plane + idx) = make_uint2(*reinterpret_cast<uint32_t*>(&l0), *reinterpret_cast<uint32_t*>(&l1));
+  store_lora16x4<__half>(p + 2 * plane, idx, plane, v);
+}
+// bf16 form only: the per-32-row "does not fit fp16" words behind the three planes
+__host__ __device__ __forceinline__ uint32_t* lora16_flags(void* base, size_t plane) {
+  return reinterpret_cast<uint32_t*>(static_cast<uint16_t*>(base) + 3 * plane);
+}
+__host__ __device__ __forceinline__ const uint32_t* lora16_flags(const void* base, size_t plane) {
+  return reinterpret_cast<const uint32_t*>(static_cast<const uint16_t*>(base) + 3 * plane);
+}
+// 16-bit elements of the whole form for `rows` x R values
+__host__ __device__ __forceinline__ size_t lora16_elems(size_t rows, size_t R, bool bf16) {
+  return bf16 ? 3 * rows * R + 2 * ((rows + 31) / 32) : rows * R;
+}
+// true if v survives the fp16 plane (finite and within range)
+__device__ __forceinline__ bool fits_f16(float4 v) {
+  return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))) <= 65504.0f;
 }
 
 // byte offset of (row m, group g) inside the 128-row x 4-group scale atoms the

@@ -224,6 +224,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   uint64_t* acc_done = bars + 2 * C::STAGES;   // MMA -> epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint32_t* lora_unfit = tmem_slot + 2;        // bf16 form: some LoRA value this CTA wrote does not fit fp16
   const WaitCtx ctx{abort_flag};
 
   // warp index through a shuffle: provably warp-uniform, so the role branches are convergent code
@@ -246,6 +247,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    *lora_unfit = 0u;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1 + QUANT_WARPS / QUANT_GROUPS); }
     mbar_init(acc_done, 1);
     fence_barrier_init();
@@ -406,10 +408,12 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
                 if (c < p.R) {
                   *reinterpret_cast<float4*>(p.lora + gm * p.R + c) =
                       make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                  if (p.lora16 != nullptr)
-                    store_lora16x4<T>(p.lora16, gm * p.R + c, static_cast<size_t>(p.M_pad) * p.R,
-                                      make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                                  __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+                  if (p.lora16 != nullptr) {
+                    const float4 o = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                                 __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                    store_lora16x4<T>(p.lora16, gm * p.R + c, static_cast<size_t>(p.M_pad) * p.R, o);
+                    if (kBf16 && !fits_f16(o)) atomicOr(lora_unfit, 1u);
+                  }
                 }
               }
             }
@@ -438,7 +442,10 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         if (c < p.R) {
           const size_t gm = static_cast<size_t>(m0 + row);
           *reinterpret_cast<float4*>(p.lora + gm * p.R + c) = acc;
-          if (p.lora16 != nullptr) store_lora16x4<T>(p.lora16, gm * p.R + c, static_cast<size_t>(p.M_pad) * p.R, acc);
+          if (p.lora16 != nullptr) {
+            store_lora16x4<T>(p.lora16, gm * p.R + c, static_cast<size_t>(p.M_pad) * p.R, acc);
+            if (kBf16 && !fits_f16(acc)) atomicOr(lora_unfit, 1u);
+          }
         }
       }
       cluster_sync_all();                                     // nobody leaves while its memory is being read
@@ -447,6 +454,13 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 
   tc_fence_before_sync();
   __syncthreads();
+  if (kBf16 && has_lora && p.lora16 != nullptr && threadIdx.x == 0) {
+    // one word per 32 rows: this CTA wrote rows [m0, m0 + 64) alone, or its 64 / KS rows of them
+    uint32_t* flags = lora16_flags(p.lora16, static_cast<size_t>(p.M_pad) * p.R);
+    const uint32_t unfit = *lora_unfit;
+    if (ks == 1) { flags[m0 / 32] = unfit; flags[m0 / 32 + 1] = unfit; }
+    else flags[m0 / 32 + krank] = unfit;
+  }
   if (*abort_flag) {
     const unsigned long long t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 50000ull) { __nanosleep(1000); }

@@ -170,6 +170,14 @@ int launch_quantize_rows(const void* x, const void* smooth, void* codes, void* s
   return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;
 }
 
+// The CUDA-core paths do not look at magnitudes: they mark every row block of a bf16 form as
+// "does not fit fp16", which sends the GEMM down its two-pass bf16 route.
+static int mark_lora16_unfit(void* out16, int rows, int R, int dtype, cudaStream_t stream) {
+  if (out16 == nullptr || dtype != SVDQ_DTYPE_BF16 || rows == 0) return SVDQ_OK;
+  uint32_t* flags = lora16_flags(out16, static_cast<size_t>(rows) * R);
+  return cudaMemsetAsync(flags, 0xFF, sizeof(uint32_t) * ((rows + 31) / 32), stream) == cudaSuccess ? SVDQ_OK : SVDQ_ERR_CUDA;
+}
+
 int launch_lora_down(const void* x, const void* w, float* out, void* out16, int M, int M_pad, int K, int R, int dtype,
                      cudaStream_t stream) {
   if (M_pad == 0 || R == 0) return SVDQ_OK;
@@ -180,7 +188,8 @@ int launch_lora_down(const void* x, const void* w, float* out, void* out16, int 
     lora_down_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), out, out16, M, M_pad, K, R);
   else
     return SVDQ_ERR_DTYPE;
-  return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;
+  if (cudaGetLastError() != cudaSuccess) return SVDQ_ERR_LAUNCH;
+  return mark_lora16_unfit(out16, M_pad, R, dtype, stream);
 }
 
 int launch_swizzle_scales(const void* src, void* dst, int groups, int rows, cudaStream_t stream) {
@@ -190,7 +199,8 @@ int launch_swizzle_scales(const void* src, void* dst, int groups, int rows, cuda
   return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;
 }
 
-int launch_cast_f32(const float* src, void* dst, long long n, int dtype, cudaStream_t stream) {
+int launch_cast_f32(const float* src, void* dst, int rows, int R, int dtype, cudaStream_t stream) {
+  const long long n = static_cast<long long>(rows) * R;
   if (n == 0) return SVDQ_OK;
   if (dtype == SVDQ_DTYPE_F16)
     cast_lora16_kernel<__half><<<grid_for(n, 256), 256, 0, stream>>>(src, dst, n);
@@ -198,7 +208,8 @@ int launch_cast_f32(const float* src, void* dst, long long n, int dtype, cudaStr
     cast_lora16_kernel<__nv_bfloat16><<<grid_for(n, 256), 256, 0, stream>>>(src, dst, n);
   else
     return SVDQ_ERR_DTYPE;
-  return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;
+  if (cudaGetLastError() != cudaSuccess) return SVDQ_ERR_LAUNCH;
+  return mark_lora16_unfit(dst, rows, R, dtype, stream);
 }
 
 }  // namespace svdq

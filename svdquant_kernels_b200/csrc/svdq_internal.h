@@ -15,7 +15,7 @@ int launch_quantize_rows(const void* x, const void* smooth, void* codes, void* s
 int launch_lora_down(const void* x, const void* w, float* out, void* out16, int M, int M_pad, int K, int R, int dtype,
                      cudaStream_t stream);
 int launch_swizzle_scales(const void* src, void* dst, int groups, int rows, cudaStream_t stream);
-int launch_cast_f32(const float* src, void* dst, long long n, int dtype, cudaStream_t stream);
+int launch_cast_f32(const float* src, void* dst, int rows, int R, int dtype, cudaStream_t stream);
 
 // quantize_fused.cu
 bool quantize_fused_supported(int M, int K, int R, int M_pad);
@@ -29,8 +29,9 @@ int quantize_fused_max_clusters(int R, int ks, int dtype);
 // gemm_w4a4.cu
 bool gemm_supported(int M, int N, int K, int R);
 int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
-                     const void* lora_act16, const void* lora_up, const void* wcscales, const void* bias, void* y,
-                     int M, int N, int K, int R, int dtype, int variant, cudaStream_t stream);
+                     const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
+                     const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant,
+                     cudaStream_t stream);
 
 // tensormap.cu : cuTensorMapEncodeTiled resolved through the runtime at first use
 enum TmapSwizzle { kTmapSwizzleNone = 0, kTmapSwizzle128 = 1 };

@@ -116,11 +116,11 @@ def quantize_w4a4_act_fuse_lora(
     lora_act = torch.empty((M_pad, R), dtype=torch.float32, device=dev)
     want_swz = M_pad % 128 == 0 and K % 64 == 0 and M_pad > 0
     swz = torch.empty(M_pad * (K // 16), dtype=torch.uint8, device=dev) if want_swz else None
-    # 16-bit form of lora_act for the GEMM: one fp16 plane, or bf16 hi and lo planes
+    # 16-bit form of lora_act for the GEMM: one fp16 plane; or bf16 hi and lo planes, an fp16 plane
+    # and the per-32-row "fits fp16" words (a flat buffer, see include/svdq_b200.h)
     la16 = None
     if R > 0:
-        shape16 = (M_pad, R) if input.dtype == torch.float16 else (2, M_pad, R)
-        la16 = torch.empty(shape16, dtype=input.dtype, device=dev)
+        la16 = torch.empty(int(lib.svdq_lora_act16_elems(M_pad, R, _DT[input.dtype])), dtype=input.dtype, device=dev)
     with torch.cuda.device(dev):
         rc = lib.svdq_quantize_w4a4_act_fuse_lora(
             _ptr(x), _ptr(ld), _ptr(sm), _ptr(table), _ptr(act), _ptr(ascales), _ptr(lora_act), _ptr(swz), _ptr(la16),
@@ -175,7 +175,7 @@ def swizzle_scales(scales: torch.Tensor) -> torch.Tensor:
 
 
 def _lora_act_16(lora_act_in: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-    """lora_act in the 16-bit form the GEMM consumes: fp16 `[M, R]`, or bf16 hi/lo planes `[2, M, R]`."""
+    """lora_act in the 16-bit form the GEMM consumes (flat; layout in include/svdq_b200.h)."""
     twin = _attached(lora_act_in)
     if twin is not None and twin.dtype == out_dtype:
         return twin
@@ -184,12 +184,26 @@ def _lora_act_16(lora_act_in: torch.Tensor, out_dtype: torch.dtype) -> torch.Ten
     src = lora_act_in if lora_act_in.dtype == torch.float32 else lora_act_in.float()
     lib = _lib.load()
     src = src.contiguous()
-    shape16 = tuple(src.shape) if out_dtype == torch.float16 else (2,) + tuple(src.shape)
-    out = torch.empty(shape16, dtype=out_dtype, device=src.device)
+    rows, R = src.shape
+    out = torch.empty(int(lib.svdq_lora_act16_elems(rows, R, _DT[out_dtype])), dtype=out_dtype, device=src.device)
     with torch.cuda.device(src.device):
-        rc = lib.svdq_cast_lora_act(_ptr(src), _ptr(out), src.numel(), _DT[out_dtype], _stream(src.device))
+        rc = lib.svdq_cast_lora_act(_ptr(src), _ptr(out), rows, R, _DT[out_dtype], _stream(src.device))
     _lib.check(rc, "cast_lora_act")
     return out
+
+
+def _lora_up_f16(lora_up: torch.Tensor) -> Optional[torch.Tensor]:
+    """fp16 copy of a bf16 lora_up (cached on the tensor) for the single-pass LoRA route of the GEMM;
+    None if a value does not fit fp16."""
+    twin = _attached(lora_up)
+    if twin is not None:
+        return twin if twin.numel() else None
+    host = lora_up.detach().cpu().contiguous()
+    out = torch.empty(host.shape, dtype=torch.float16)
+    rc = _lib.load().svdq_lora_up_to_f16(_ptr(host), _ptr(out), host.numel())
+    dev_copy = out.to(lora_up.device) if rc == _lib.OK else torch.empty(0, dtype=torch.float16, device=lora_up.device)
+    _attach(lora_up, dev_copy)
+    return dev_copy if dev_copy.numel() else None
 
 
 def gemm_w4a4(
@@ -252,15 +266,17 @@ def gemm_w4a4(
     w = wgt.contiguous()
     sa = swizzle_scales(ascales)
     sw = swizzle_scales(wscales)
-    la = lu = None
+    la = lu = lu16 = None
     if R > 0:
         la = _lora_act_16(lora_act_in, out_dtype)
         lu = lora_up.contiguous()
+        if out_dtype == torch.bfloat16:
+            lu16 = _lora_up_f16(lu)
     wc = None if wcscales is None else wcscales.to(out_dtype).contiguous()
     b = None if bias is None else bias.to(out_dtype).contiguous()
     y = torch.empty((M, N), dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
-        rc = lib.svdq_gemm_w4a4(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(wc), _ptr(b), _ptr(y),
+        rc = lib.svdq_gemm_w4a4(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc), _ptr(b), _ptr(y),
                                 M, N, K, R, _DT[out_dtype], variant, _stream(dev))
     _lib.check(rc, "gemm_w4a4")
     return y

@@ -55,10 +55,22 @@ def test_argument_validation_needs_no_device(lib_path):
     assert lib.svdq_gemm_w4a4_supported(100, 128, 128, 16) == 0
     assert lib.svdq_gemm_w4a4_supported(256, 128, 96, 16) == 0
     assert lib.svdq_gemm_w4a4_supported(256, 128, 128, 8) == 0
-    assert lib.svdq_gemm_w4a4(p, p, p, p, None, None, None, None, p, 100, 128, 128, 0, 0, 0, None) == 2
-    assert lib.svdq_gemm_w4a4(p, p, p, p, p, None, None, None, p, 128, 128, 128, 16, 0, 0, None) == 1
-    assert lib.svdq_gemm_w4a4(p, p, p, p, None, None, None, None, p, 128, 128, 128, 0, 5, 0, None) == 3
+    assert lib.svdq_gemm_w4a4(p, p, p, p, None, None, None, None, None, p, 100, 128, 128, 0, 0, 0, None) == 2
+    assert lib.svdq_gemm_w4a4(p, p, p, p, p, None, None, None, None, p, 128, 128, 128, 16, 0, 0, None) == 1
+    assert lib.svdq_gemm_w4a4(p, p, p, p, None, None, None, None, None, p, 128, 128, 128, 0, 5, 0, None) == 3
     assert lib.svdq_swizzle_scales(p, p, 6, 128, None) == 2
+    # sizes of the 16-bit lora_act form: one plane for fp16; three planes + a word per 32 rows for bf16
+    assert lib.svdq_lora_act16_elems(256, 32, 0) == 256 * 32
+    assert lib.svdq_lora_act16_elems(256, 32, 1) == 3 * 256 * 32 + 2 * 8
+    assert lib.svdq_lora_act16_elems(-1, 32, 1) == -1
+    # host-side bf16 -> fp16 copy of lora_up: exact for ordinary values, refused beyond fp16's range
+    import numpy as np
+    src = np.array([0x3F80, 0xBC00, 0x0000, 0x4000], dtype=np.uint16)          # 1.0, -0.0078125, 0, 2.0 as bf16
+    dst = np.zeros(4, dtype=np.float16)
+    assert lib.svdq_lora_up_to_f16(src.ctypes.data, dst.ctypes.data, 4) == 0
+    assert dst.tolist() == [1.0, -0.0078125, 0.0, 2.0]
+    big = np.array([0x4800], dtype=np.uint16)                                   # 131072 as bf16
+    assert lib.svdq_lora_up_to_f16(big.ctypes.data, dst.ctypes.data, 1) == 7
 
 
 def test_operator_asserts_mirror_the_reference(lib_path):

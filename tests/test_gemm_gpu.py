@@ -134,3 +134,43 @@ def test_largest_configs_whole_output(cfg):
     d = (y.float() - ref).reshape(y.shape[0] // 256, 256, y.shape[1] // 256, 256).pow(2).sum((1, 3)).sqrt()
     n = ref.reshape(y.shape[0] // 256, 256, y.shape[1] // 256, 256).pow(2).sum((1, 3)).sqrt()
     assert (d / n).max().item() <= 2 * TOL
+
+
+def test_bf16_lora_routes(monkeypatch):
+    """bf16 output: tiles whose lora_act rows all fit fp16 take one fp16 LoRA pass, the others the
+    hi + lo bf16 passes.  Rows 512..575 are blown up past 65504 so that one 256-row tile of the four
+    must fall back; every route has to stay inside the tolerance, and so has the all-bf16 route
+    (no fp16 copy of lora_up)."""
+    ops = _ops()
+    dtype, M, K, N, R = torch.bfloat16, 1024, 512, 512, 64
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(M, K, generator=g)
+    x[512:576] *= 3000.0
+    x = x.to(dtype)
+    sm = (torch.rand(K, generator=g) + 0.5).to(dtype)
+    w = torch.randn(N, K, generator=g) * 0.02 / sm.float()[None, :]
+    ld = torch.randn(K, R, generator=g).to(dtype)                     # large on purpose: lora_act ~ 3000 * 22
+    lu = (torch.randn(N, R, generator=g) * 0.01).to(dtype)
+    dev = "cuda"
+    act, asc, la = ops.quantize_w4a4_act_fuse_lora(x.to(dev), ld.to(dev), sm.to(dev))
+    blocks = la.abs().reshape(M // 32, -1).amax(1).cpu()
+    assert (blocks[16:18] > 65504).all() and (blocks[:16] < 65504).all() and (blocks[18:] < 65504).all()
+    wgt, wsc = ops.quantize_nvfp4_rows(w.to(dev), pad_size=1)
+    y_bits, _ = oracle_gemm(u8(act), u8(wgt), u8(asc), u8(wsc), la.cpu().numpy(), lu, None, None, dtype)
+
+    y_mixed = ops.gemm_w4a4(act, wgt, asc, wsc, la, lu.to(dev), None, None, dtype)
+    torch.cuda.synchronize()
+    assert_device_clean()
+    assert rel_l2_vs_bits(y_mixed, y_bits) <= TOL
+    # per 256-row tile as well: the fallback tile (rows 512..767) must not hide behind the others
+    for t in range(4):
+        rows = slice(256 * t, 256 * t + 256)
+        assert rel_l2_vs_bits(y_mixed[rows], y_bits[rows]) <= TOL, f"tile {t}"
+
+    monkeypatch.setattr(ops, "_lora_up_f16", lambda t: None)
+    y_bf16 = ops.gemm_w4a4(act, wgt, asc, wsc, la, lu.to(dev), None, None, dtype)
+    torch.cuda.synchronize()
+    assert_device_clean()
+    assert rel_l2_vs_bits(y_bf16, y_bits) <= TOL
+    # the fallback tile ran the same instructions on the same data in both launches
+    assert torch.equal(y_bf16[512:768], y_mixed[512:768])

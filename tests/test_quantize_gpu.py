@@ -40,14 +40,26 @@ def _check(x, ld, sm, force, pad=256):
     twin16 = getattr(lora, "_svdq_twin", None)
     if twin16 is not None and ld.shape[1] > 0:
         la = lora.cpu().numpy()
+        want16 = O.f32_to_bits(np.clip(la, -65504.0, 65504.0), "fp16")
         if x.dtype == torch.float16:
-            want = O.f32_to_bits(np.clip(la, -65504.0, 65504.0), "fp16")
-            assert (bits(twin16[0]) == want).all(), "fp16 lora_act is not the rounded fp32 one"
+            assert (bits(twin16[0]).reshape(la.shape) == want16).all(), "fp16 lora_act is not the rounded fp32 one"
         else:
+            # flat: hi plane, lo plane, fp16 plane, then one 32-bit word per 32 rows (0 = fits fp16)
             hi = O.f32_to_bits(la, "bf16")
             lo = O.f32_to_bits(la - O.bits_to_f32(hi, "bf16"), "bf16")
             got = bits(twin16[0])
-            assert (got[0] == hi).all() and (got[1] == lo).all(), "bf16 hi/lo planes of lora_act differ"
+            n = la.size
+            assert (got[:n].reshape(la.shape) == hi).all() and (got[n:2 * n].reshape(la.shape) == lo).all(), \
+                "bf16 hi/lo planes of lora_act differ"
+            assert (got[2 * n:3 * n].reshape(la.shape) == want16).all(), "fp16 plane of lora_act differs"
+            flags = got[3 * n:].astype(np.uint32)
+            flags = flags[0::2] | (flags[1::2] << 16)
+            blocks = -(-la.shape[0] // 32)
+            unfit = np.array([not (np.abs(la[32 * b:32 * b + 32]) <= 65504.0).all() for b in range(blocks)])
+            if force == FUSED:
+                assert ((flags[:blocks] != 0) == unfit).all(), "fits-fp16 words of lora_act differ"
+            else:
+                assert (flags[:blocks] != 0).all(), "the CUDA-core path must mark every row block"
     return act, ascales, lora
 
 
