@@ -121,6 +121,9 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
   return ok != 0;
 }
 
+#ifndef SVDQ_WAIT_HINT_NS
+#define SVDQ_WAIT_HINT_NS 2000u   // how long a waiting thread may be parked per poll
+#endif
 #ifndef SVDQ_WAIT_LIMIT_NS
 #define SVDQ_WAIT_LIMIT_NS 400000000ull  // 0.4 s: orders of magnitude above any legitimate wait here
 #endif
@@ -133,7 +136,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
   unsigned long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+    if (mbar_try_wait_hint(bar, parity, SVDQ_WAIT_HINT_NS)) return true;
     if (*ctx.abort_flag) return false;
     if ((++spins & 0x3F) == 0) {
       unsigned long long now = globaltimer_ns();
