@@ -87,7 +87,9 @@ def build_case(name, M, K, N, R, dtype, seed, with_smooth=True, edge=False):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to a checkout of the reference>")
+    ref = sys.argv[1]
     sys.path.insert(0, ref)
     from baseline.kernels._nvfp4 import dequantize_nvfp4_rows, quantize_nvfp4_rows
     from baseline.kernels.gemm_w4a4.ref import gemm_w4a4_ref
