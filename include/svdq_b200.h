@@ -147,6 +147,24 @@ int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, co
                    const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales, const void* bias,
                    void* y, int M, int N, int K, int R, int dtype, int variant, void* stream);
 
+/*
+ * Column-sharded (tensor-parallel) form of svdq_gemm_w4a4, one call per GPU: this GPU holds rows
+ * [col0, col0 + N) of wgt / wscales / lora_up / wcscales / bias and computes those columns of the
+ * [M, N_total] result.  Every finished 32 x 64 strip is written into y_full (this GPU's copy of the
+ * whole result) and, with plain stores over NVLink, into the same place of y_full_peers[0 ..
+ * n_peers-1] (device pointers to the other GPUs' copies, mapped into this process: symmetric
+ * memory, CUDA IPC or cuMemMap), so the all-gather the sharding needs rides on the GEMM's epilogue
+ * instead of following it.  The caller orders the ranks around the call: nobody may still read its
+ * y_full when a peer starts, and a rank reads its y_full only after every peer's launch has
+ * completed (a stream barrier over the ranks on either side).  col0 % 64 == 0, N_total % 8 == 0,
+ * n_peers <= 7.  No counterpart in the reference, which has no multi-GPU code.
+ */
+int svdq_gemm_w4a4_columns(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                           const void* lora_act16, const void* lora_up, const void* lora_up_f16,
+                           const void* wcscales, const void* bias, void* y_full, void* const* y_full_peers,
+                           int n_peers, int N_total, int col0, int M, int N, int K, int R, int dtype,
+                           int variant, void* stream);
+
 /* 1 if (M, N, K, R) is inside the GEMM contract, else 0. */
 int svdq_gemm_w4a4_supported(int M, int N, int K, int R);
 

@@ -31,6 +31,7 @@ SIGNATURES = {
     "svdq_cast_lora_act": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "svdq_lora_up_to_f16": (c_int, [c_void_p, c_void_p, c_longlong]),
     "svdq_gemm_w4a4": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p]),
+    "svdq_gemm_w4a4_columns": (c_int, [c_void_p] * 10 + [POINTER(c_void_p)] + [c_int] * 9 + [c_void_p]),
     "svdq_gemm_w4a4_supported": (c_int, [c_int, c_int, c_int, c_int]),
     "svdq_device_status": (c_int, [POINTER(c_uint)]),
     "svdq_linear_plan_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int] + [c_void_p] * 7),

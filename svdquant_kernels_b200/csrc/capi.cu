@@ -150,7 +150,34 @@ int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, co
       !aligned16(lora_act16) || !aligned16(lora_up) || !aligned16(lora_up_f16) || !aligned16(y))
     return SVDQ_ERR_ALIGN;
   return launch_gemm_w4a4(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N,
-                          K, R, dtype, variant, static_cast<cudaStream_t>(stream));
+                          K, R, dtype, variant, GemmTp(), static_cast<cudaStream_t>(stream));
+}
+
+int svdq_gemm_w4a4_columns(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                           const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
+                           const void* bias, void* y_full, void* const* y_full_peers, int n_peers, int N_total,
+                           int col0, int M, int N, int K, int R, int dtype, int variant, void* stream) {
+  if (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16) return SVDQ_ERR_DTYPE;
+  if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
+  if (act == nullptr || wgt == nullptr || ascales_swz == nullptr || wscales_swz == nullptr || y_full == nullptr)
+    return SVDQ_ERR_NULL;
+  if ((lora_act16 == nullptr) != (lora_up == nullptr)) return SVDQ_ERR_NULL;
+  if (R > 0 && lora_act16 == nullptr) return SVDQ_ERR_NULL;
+  if (lora_act16 == nullptr) R = 0;
+  if (n_peers < 0 || n_peers > 7 || (n_peers > 0 && y_full_peers == nullptr)) return SVDQ_ERR_SHAPE;
+  if (N_total < N || col0 < 0 || col0 + N > N_total) return SVDQ_ERR_SHAPE;
+  if (!aligned16(act) || !aligned16(wgt) || !aligned16(ascales_swz) || !aligned16(wscales_swz) ||
+      !aligned16(lora_act16) || !aligned16(lora_up) || !aligned16(lora_up_f16) || !aligned16(y_full))
+    return SVDQ_ERR_ALIGN;
+  GemmTp tp;
+  tp.col0 = col0; tp.y_ld = N_total; tp.n_peers = n_peers;
+  for (int d = 0; d < n_peers; ++d) {
+    if (y_full_peers[d] == nullptr) return SVDQ_ERR_NULL;
+    if (!aligned16(y_full_peers[d])) return SVDQ_ERR_ALIGN;
+    tp.y_peer[d] = y_full_peers[d];
+  }
+  return launch_gemm_w4a4(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y_full,
+                          M, N, K, R, dtype, variant, tp, static_cast<cudaStream_t>(stream));
 }
 
 int svdq_device_status(unsigned int out[4]) {

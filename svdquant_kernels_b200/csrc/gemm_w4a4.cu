@@ -101,6 +101,12 @@ struct Params {
   const uint32_t* la_flags;   // bf16 only: per 32 rows of lora_act, non-zero = does not fit fp16; null = always two-pass
   int M, N, K, R;
   int tiles_m, tiles_n; // in units of (CG*128) x BN
+  // Column-sharded (tensor-parallel) form: this launch computes columns [col0, col0 + N) of a
+  // [M, y_ld] result that every rank holds in full.  The local copy is written through tmY (built over
+  // the local full matrix); each finished strip is also stored, with plain 16-byte stores straight
+  // from the staging buffer, into the same place of every peer's matrix (peer-mapped memory).
+  int col0, y_ld, n_peers;
+  void* y_peer[7];
 };
 
 __device__ __forceinline__ uint32_t pack2(__half a, __half b) {
@@ -429,8 +435,28 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(&tmY, buf, n0 + cbase, m0 + quarter * 32);
+          tma_store_2d(&tmY, buf, p.col0 + n0 + cbase, m0 + quarter * 32);
           tma_store_commit();
+        }
+        if (p.n_peers > 0) {
+          // the strip is 32 rows x 128 bytes in the staging buffer (16-byte chunks XOR-swizzled by row);
+          // eight lanes carry one row, so every store instruction writes four whole 128-byte lines
+          const uint32_t chunk = static_cast<uint32_t>(lane & 7);
+          uint4 part[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t r = static_cast<uint32_t>(4 * i + (lane >> 3));
+            part[i] = *reinterpret_cast<const uint4*>(buf + r * 128 + ((chunk ^ (r & 7u)) << 4));
+          }
+          const size_t col = static_cast<size_t>(p.col0 + n0 + cbase) + chunk * 8;
+          for (int d = 0; d < p.n_peers; ++d) {
+            OutT* dst = static_cast<OutT*>(p.y_peer[d]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const size_t row = static_cast<size_t>(m0 + quarter * 32 + 4 * i + (lane >> 3));
+              *reinterpret_cast<uint4*>(dst + row * p.y_ld + col) = part[i];
+            }
+          }
         }
       }
       // affine[] may be overwritten after this barrier; it also makes the eight warps agree on whether to go on
@@ -470,7 +496,7 @@ bool gemm_supported(int M, int N, int K, int R) {
 template <int CG, int BN, typename OutT>
 static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, const void* sfb, const void* la,
                          const void* lu, const void* lu_f16, const void* wc, const void* bias, void* y, int M, int N,
-                         int K, int R, cudaStream_t stream) {
+                         int K, int R, const GemmTp& tp, cudaStream_t stream) {
   using C = gemm::Cfg<CG, BN>;
   constexpr bool kBf16 = std::is_same<OutT, __nv_bfloat16>::value;
   CUtensorMap tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, tmLAf, tmLUf;
@@ -480,7 +506,8 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   if ((rc = make_tmap_2d(&tmSFB, sfb, 4, (N / 128) * atoms_k, 128, 512, 4, 128, kTmapSwizzleNone)) != SVDQ_OK) return rc;
   if ((rc = make_tmap_2d(&tmA, act, 1, M, K / 2, K / 2, gemm::BM, 128, kTmapSwizzle128)) != SVDQ_OK) return rc;
   if ((rc = make_tmap_2d(&tmB, wgt, 1, N, K / 2, K / 2, C::B_ROWS, 128, kTmapSwizzle128)) != SVDQ_OK) return rc;
-  if ((rc = make_tmap_2d(&tmY, y, 2, M, N, static_cast<uint64_t>(N) * 2, 32, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
+  const int y_ld = tp.y_ld > 0 ? tp.y_ld : N;      // y may be the [M, y_ld] matrix this launch fills N columns of
+  if ((rc = make_tmap_2d(&tmY, y, 2, M, y_ld, static_cast<uint64_t>(y_ld) * 2, 32, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
   if (R > 0) {
     const uint64_t la_rows = static_cast<uint64_t>(M) * (std::is_same<OutT, __nv_bfloat16>::value ? 2 : 1);
     if ((rc = make_tmap_2d(&tmLA, la, 2, la_rows, R, static_cast<uint64_t>(R) * 2, gemm::BM, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
@@ -502,6 +529,8 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   p.wc = wc; p.bias = bias;
   p.M = M; p.N = N; p.K = K; p.R = R;
   p.tiles_m = M / (gemm::BM * CG); p.tiles_n = N / BN;
+  p.col0 = tp.y_ld > 0 ? tp.col0 : 0; p.y_ld = y_ld; p.n_peers = tp.n_peers;
+  for (int d = 0; d < 7; ++d) p.y_peer[d] = d < tp.n_peers ? tp.y_peer[d] : nullptr;
   auto kern = gemm::gemm_w4a4_kernel<CG, BN, OutT>;
   static bool configured = false;
   if (!configured) {
@@ -530,19 +559,22 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
 template <typename OutT>
 static int launch_gemm_dt(int cg, int bn, const void* act, const void* wgt, const void* sfa, const void* sfb,
                           const void* la, const void* lu, const void* lu_f16, const void* wc, const void* bias, void* y,
-                          int M, int N, int K, int R, cudaStream_t stream) {
-  if (cg == 2 && bn == 256) return launch_gemm_t<2, 256, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, stream);
-  if (cg == 2 && bn == 128) return launch_gemm_t<2, 128, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, stream);
-  if (cg == 1 && bn == 256) return launch_gemm_t<1, 256, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, stream);
-  return launch_gemm_t<1, 128, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, stream);
+                          int M, int N, int K, int R, const GemmTp& tp, cudaStream_t stream) {
+  if (cg == 2 && bn == 256) return launch_gemm_t<2, 256, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
+  if (cg == 2 && bn == 128) return launch_gemm_t<2, 128, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
+  if (cg == 1 && bn == 256) return launch_gemm_t<1, 256, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
+  return launch_gemm_t<1, 128, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
 }
 
 // variant: 0 = choose; 128 / 256 = one CTA per tile with that N tile; 2128 / 2256 = CTA pairs (256-row tiles)
 int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
                      const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
                      const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant,
-                     cudaStream_t stream) {
+                     const GemmTp& tp, cudaStream_t stream) {
   if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
+  if (tp.n_peers < 0 || tp.n_peers > 7) return SVDQ_ERR_SHAPE;
+  if (tp.y_ld > 0 && (tp.col0 < 0 || tp.col0 % 64 != 0 || tp.col0 + N > tp.y_ld || tp.y_ld % 8 != 0)) return SVDQ_ERR_SHAPE;
+  if (tp.y_ld <= 0 && tp.n_peers > 0) return SVDQ_ERR_SHAPE;
   int cg, bn;
   if (variant == 0) {
     cg = (M % 256 == 0) ? 2 : 1;
@@ -555,9 +587,9 @@ int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, 
   if ((cg != 1 && cg != 2) || (bn != 128 && bn != 256)) return SVDQ_ERR_UNSUPPORTED;
   if (M % (128 * cg) != 0 || N % bn != 0) return SVDQ_ERR_SHAPE;
   if (dtype == SVDQ_DTYPE_F16)
-    return launch_gemm_dt<__half>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, nullptr, wcscales, bias, y, M, N, K, R, stream);
+    return launch_gemm_dt<__half>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, nullptr, wcscales, bias, y, M, N, K, R, tp, stream);
   if (dtype == SVDQ_DTYPE_BF16)
-    return launch_gemm_dt<__nv_bfloat16>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R, stream);
+    return launch_gemm_dt<__nv_bfloat16>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R, tp, stream);
   return SVDQ_ERR_DTYPE;
 }
 

@@ -28,10 +28,16 @@ int quantize_fused_max_clusters(int R, int ks, int dtype);
 
 // gemm_w4a4.cu
 bool gemm_supported(int M, int N, int K, int R);
+// Column-sharded form: y is the local [M, y_ld] matrix, this launch fills columns [col0, col0 + N)
+// of it and of the same matrix of n_peers other GPUs (peer-mapped pointers).  y_ld = 0: plain call.
+struct GemmTp {
+  int col0 = 0, y_ld = 0, n_peers = 0;
+  void* y_peer[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+};
 int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
                      const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
                      const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant,
-                     cudaStream_t stream);
+                     const GemmTp& tp, cudaStream_t stream);
 
 // tensormap.cu : cuTensorMapEncodeTiled resolved through the runtime at first use
 enum TmapSwizzle { kTmapSwizzleNone = 0, kTmapSwizzle128 = 1 };

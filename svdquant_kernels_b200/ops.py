@@ -220,7 +220,12 @@ def gemm_w4a4(
     use_2cta: bool = False,                 # accepted for call-site compatibility
     tiler_mn: Optional[Tuple[int, int]] = None,
     lora_schedule: str = "interleave",
+    _columns: Optional[Tuple[torch.Tensor, list, int]] = None,
 ) -> torch.Tensor:
+    """`_columns = (y_full, peer_ptrs, col0)` selects the column-sharded form (svdq_gemm_w4a4_columns):
+    the `[M, N]` result of this call goes into columns `[col0, col0 + N)` of the local `[M, N_total]`
+    tensor `y_full` and of the peers' copies at the raw device pointers `peer_ptrs`; `y_full` is
+    returned.  See `sharding.linear_columns_fused` for the ordering the caller owes."""
     if out_dtype is None:
         out_dtype = lora_up.dtype if lora_up is not None else torch.float16
     assert act.is_cuda and wgt.is_cuda and ascales.is_cuda and wscales.is_cuda, "all inputs must live on CUDA"
@@ -274,6 +279,19 @@ def gemm_w4a4(
             lu16 = _lora_up_f16(lu)
     wc = None if wcscales is None else wcscales.to(out_dtype).contiguous()
     b = None if bias is None else bias.to(out_dtype).contiguous()
+    if _columns is not None:
+        import ctypes
+        y_full, peer_ptrs, col0 = _columns
+        assert y_full.is_cuda and y_full.is_contiguous() and y_full.dtype == out_dtype and y_full.shape[0] == M
+        n_total = y_full.shape[1]
+        assert 0 <= col0 and col0 + N <= n_total and col0 % 64 == 0 and len(peer_ptrs) <= 7
+        arr = (ctypes.c_void_p * max(1, len(peer_ptrs)))(*peer_ptrs)
+        with torch.cuda.device(dev):
+            rc = lib.svdq_gemm_w4a4_columns(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc),
+                                            _ptr(b), _ptr(y_full), arr, len(peer_ptrs), n_total, col0, M, N, K, R,
+                                            _DT[out_dtype], variant, _stream(dev))
+        _lib.check(rc, "gemm_w4a4_columns")
+        return y_full
     y = torch.empty((M, N), dtype=out_dtype, device=dev)
     with torch.cuda.device(dev):
         rc = lib.svdq_gemm_w4a4(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc), _ptr(b), _ptr(y),
