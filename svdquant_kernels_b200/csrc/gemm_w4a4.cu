@@ -577,8 +577,22 @@ int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, 
   if (tp.y_ld <= 0 && tp.n_peers > 0) return SVDQ_ERR_SHAPE;
   int cg, bn;
   if (variant == 0) {
-    cg = (M % 256 == 0) ? 2 : 1;
-    bn = (N % 256 == 0) ? 256 : 128;
+    // Pick the tile shape with the least estimated time: waves of tiles over the SMs (or SM pairs)
+    // times the measured relative time of one tile (a 128-column tile takes 0.72 of a 256-column
+    // one, not half: it moves more operand bytes per flop; a single CTA per tile takes 1.12 of a
+    // pair's time for loading all of B itself).  Large problems end on 256 x 256 pair tiles, a few
+    // hundred rows on narrower tiles that put more SMs to work.
+    const int sms = sm_count();
+    double best = 1e30;
+    cg = 1; bn = 128;
+    for (int c : {2, 1})
+      for (int b : {256, 128}) {
+        if (M % (128 * c) != 0 || N % b != 0) continue;
+        const long long tiles = static_cast<long long>(M / (128 * c)) * (N / b);
+        const long long units = sms / c;
+        const double cost = static_cast<double>((tiles + units - 1) / units) * (b == 256 ? 1.0 : 0.72) * (c == 2 ? 1.0 : 1.12);
+        if (cost < best) { best = cost; cg = c; bn = b; }
+      }
   } else if (variant == 128 || variant == 256) {
     cg = 1; bn = variant;
   } else {
