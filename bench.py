@@ -117,8 +117,18 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # all host cores, also under torchrun (which exports OMP_NUM_THREADS=1 to every rank)
+    ncpu = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[var] = str(ncpu)
     import numpy as np
     import torch
+    torch.set_num_threads(ncpu)
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=ncpu)
+    except Exception:
+        pass
     from oracle import nvfp4_oracle as O
     from svdquant_kernels_b200.workloads import CONFIGS, make_inputs
     shape = CONFIGS[args.config]
