@@ -43,6 +43,14 @@
 // fp16 as one rounded copy, bf16 as a hi + lo pair (lora_act = hi + lo to 16
 // significant bits) that takes two passes over the same lora_up slab - a single
 // bf16 copy would put the LoRA term's 2^-9 rounding error above the 1e-3 bound.
+// For bf16 the quantizer also provides lora_act as an fp16 plane with a word per 32
+// rows telling whether those rows fit fp16; given an fp16 copy of lora_up, a tile
+// whose rows all fit takes a single fp16 pass instead (decided per tile by every
+// role from the same words, so all agree on the tile's slab count).
+//
+// Column-sharded form (n_peers > 0): the launch fills N columns of a wider result
+// that every GPU holds in full; each finished strip is also written, with plain
+// 16-byte stores from the staging buffer, into the peers' copies over NVLink.
 #include "nvfp4_math.cuh"
 #include "sm100.cuh"
 #include "svdq_internal.h"
