@@ -540,10 +540,13 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   p.col0 = tp.y_ld > 0 ? tp.col0 : 0; p.y_ld = y_ld; p.n_peers = tp.n_peers;
   for (int d = 0; d < 7; ++d) p.y_peer[d] = d < tp.n_peers ? tp.y_peer[d] : nullptr;
   auto kern = gemm::gemm_w4a4_kernel<CG, BN, OutT>;
-  static bool configured = false;
-  if (!configured) {
+  // the attribute is per device: remember which devices of this process have it
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return SVDQ_ERR_CUDA;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return SVDQ_ERR_LAUNCH;
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int max_pairs = sm_count() / CG;

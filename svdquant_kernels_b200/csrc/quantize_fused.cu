@@ -92,16 +92,25 @@ struct Params {
   int M, K, R, M_pad;
 };
 
-template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t v);
-// Both widen a pair after adding +0, which turns -0 into +0 and changes nothing else: the
-// reference gives a zero the sign bit only when the value tests < 0.
-template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t v) {
+// Widen a pair of 16-bit values.  CANON adds +0 first, which turns -0 into +0 and changes nothing else
+// (the reference gives a zero the sign bit only when the value tests < 0).  The smoothing divide of
+// the fast path does the same by itself - for s > 0, q0 = x r keeps the zero's sign, e =
+// fma(-s, q0, x) is +0 and q = fma(e, r, q0) = +0 for either zero - so only the other paths ask
+// for it.
+template <typename T, bool CANON> __device__ __forceinline__ float2 unpack2(uint32_t v);
+template <> __device__ __forceinline__ float2 unpack2<__half, true>(uint32_t v) {
   return __half22float2(__hadd2(*reinterpret_cast<__half2*>(&v), __float2half2_rn(0.0f)));
 }
-template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t v) {
+template <> __device__ __forceinline__ float2 unpack2<__half, false>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16, true>(uint32_t v) {
   const __nv_bfloat162 c = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&v), __float2bfloat162_rn(0.0f));
   const uint32_t u = *reinterpret_cast<const uint32_t*>(&c);
   return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16, false>(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
 }
 
 // float4 slot of (row, c4) in the partial-accumulator buffer; the XOR spreads the
@@ -110,12 +119,12 @@ __device__ __forceinline__ uint32_t partial_slot(uint32_t row, uint32_t c4, uint
   return row * rp4 + (c4 ^ (row & 7u));
 }
 
-template <typename T>
+template <typename T, bool CANON>
 __device__ __forceinline__ void unpack_group(const uint4& lo16, const uint4& hi16, float (&f)[16]) {
   const uint32_t w[8] = {lo16.x, lo16.y, lo16.z, lo16.w, hi16.x, hi16.y, hi16.z, hi16.w};
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    const float2 v = unpack2<T>(w[j]);
+    const float2 v = unpack2<T, CANON>(w[j]);
     f[2 * j] = v.x; f[2 * j + 1] = v.y;
   }
 }
@@ -343,8 +352,13 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         raw[rr][1] = *reinterpret_cast<const uint4*>(xrow + (((2 * g + 1) ^ (row & 7)) << 4));
       }
       float f[2][16];
-      unpack_group<T>(raw[0][0], raw[0][1], f[0]);
-      unpack_group<T>(raw[1][0], raw[1][1], f[1]);
+      if (has_table && !use_fdiv) {
+        unpack_group<T, false>(raw[0][0], raw[0][1], f[0]);
+        unpack_group<T, false>(raw[1][0], raw[1][1], f[1]);
+      } else {
+        unpack_group<T, true>(raw[0][0], raw[0][1], f[0]);
+        unpack_group<T, true>(raw[1][0], raw[1][1], f[1]);
+      }
       if (has_table) {
         // {smooth, 1/smooth} of this lane's 16 columns landed with the slab
         const float4* tb = reinterpret_cast<const float4*>(st + X_BYTES + C::W_BYTES + g * TB_GROUP_STRIDE);
@@ -472,8 +486,9 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   }
 }
 
-// {smooth, 1/smooth} per column, then one flag word: 1 if any |smooth| lies outside
-// [2^-60, 2^60] (or is NaN), where the three-step divide could over- or underflow.
+// {smooth, 1/smooth} per column, then one flag word: 1 if any smooth value lies outside
+// [2^-60, 2^60] (2^16 for bf16; negative, zero and NaN count as outside), where the three-step divide
+// could over- or underflow or leave a zero with the wrong sign.
 template <typename T>
 __global__ void smooth_table_kernel(const T* __restrict__ smooth, float2* __restrict__ table, int K) {
   // upper bound: 2^60 for fp16 inputs; 2^16 for bf16 inputs, whose smallest subnormal (2^-133)
@@ -485,8 +500,7 @@ __global__ void smooth_table_kernel(const T* __restrict__ smooth, float2* __rest
   for (int i = threadIdx.x; i < K; i += blockDim.x) {
     const float s = to_f32(smooth[i]);
     table[i] = make_float2(s, __frcp_rn(s));
-    const float a = fabsf(s);
-    if (!(a >= 8.6736174e-19f && a <= kMaxSmooth)) bad = 1;
+    if (!(s >= 8.6736174e-19f && s <= kMaxSmooth)) bad = 1;      // also: negative, zero or NaN
   }
   __syncthreads();
   if (threadIdx.x == 0) *reinterpret_cast<uint2*>(table + K) = make_uint2(bad ? 1u : 0u, 0u);
@@ -540,10 +554,13 @@ static int launch_qf(const void* x, const void* w, const qf::Params& p, cudaStre
     tmW = tmX;
   }
   auto kern = qf::quantize_fused_kernel<T, RP>;
-  static bool configured = false;
-  if (!configured) {
+  // the attribute is per device: remember which devices of this process have it
+  static bool configured[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return SVDQ_ERR_CUDA;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return SVDQ_ERR_LAUNCH;
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   int ks = pick_k_split(p.M_pad, p.K);
   cudaLaunchConfig_t cfg = {};

@@ -180,3 +180,33 @@ def test_row_permutation_property_full_size():
     assert (u8(a1)[rows.numpy()] == o_act).all()
     assert (u8(s1)[:, rows.numpy()] == o_sc).all()
     assert O.rel_l2(l1.cpu().numpy()[rows.numpy()], o_lora) <= LORA_TOL
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("smooth_kind", ["positive", "none", "some_negative"])
+def test_signed_zeros_and_negative_smooth(dtype, smooth_kind):
+    """-0.0 inputs must come out with code 0 (the reference sets the sign bit only for values < 0), also
+    next to tiny negative values (code 8) in the same group, and a smooth vector with negative entries
+    (outside the fast divide's domain) must still be bit-exact."""
+    M, K, R = 128, 256, 16
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(M, K, generator=g)
+    x[:, 0:16] = 0.0
+    x[::2, 0:16] = -0.0
+    x[:, 16:32] = -0.0
+    x[:, 16] = 3.0                      # a group of -0 with one real value: non-zero scale
+    x[:, 32:48] *= 1e-4
+    x[1::3, 40] = -0.0
+    x = x.to(dtype)
+    ld = (torch.randn(K, R, generator=g) / K ** 0.5).to(dtype)
+    if smooth_kind == "none":
+        sm = None
+    else:
+        sm = (torch.rand(K, generator=g) + 0.5)
+        if smooth_kind == "some_negative":
+            sm[5] = -sm[5]
+            sm[17] = -sm[17]
+            sm[200] = -sm[200]
+        sm = sm.to(dtype).cuda()
+    _check(x.cuda(), ld.cuda(), sm, FUSED)
+    _check(x.cuda(), ld.cuda(), sm, GENERIC)
