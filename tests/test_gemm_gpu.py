@@ -174,3 +174,33 @@ def test_bf16_lora_routes(monkeypatch):
     assert rel_l2_vs_bits(y_bf16, y_bits) <= TOL
     # the fallback tile ran the same instructions on the same data in both launches
     assert torch.equal(y_bf16[512:768], y_mixed[512:768])
+
+
+def test_back_to_back_steps_keep_their_results():
+    """Both kernels start their set-up before the kernel ahead of them has finished (programmatic
+    dependent launch) and PyTorch hands freed buffers straight to the next call, so a chain of steps
+    with no host synchronisation in between is the pattern that would expose a missing dependency:
+    every step's y must equal the y of the same step run alone."""
+    ops = _ops()
+    dtype, M, K, N, R = torch.float16, 1024, 1024, 512, 64
+    g = torch.Generator().manual_seed(5)
+    sm = (torch.rand(K, generator=g) + 0.5).to(dtype).cuda()
+    ld = (torch.randn(K, R, generator=g) / K ** 0.5).to(dtype).cuda()
+    lu = (torch.randn(N, R, generator=g) * 0.01).to(dtype).cuda()
+    wgt, wsc = ops.quantize_nvfp4_rows((torch.randn(N, K, generator=g) * 0.02).cuda(), pad_size=1)
+    xs = [torch.randn(M, K, generator=g).to(dtype).cuda() for _ in range(12)]
+
+    def step(x):
+        act, asc, la = ops.quantize_w4a4_act_fuse_lora(x, ld, sm)
+        return ops.gemm_w4a4(act, wgt, asc, wsc, la, lu, None, None, dtype)
+
+    alone = []
+    for x in xs:
+        alone.append(step(x))
+        torch.cuda.synchronize()
+    for rep in range(3):
+        chained = [step(x) for x in xs]          # 24 launches queued back to back
+        torch.cuda.synchronize()
+        for i, (a, c) in enumerate(zip(alone, chained)):
+            assert torch.equal(a, c), f"repetition {rep}, step {i}"
+    assert_device_clean()
