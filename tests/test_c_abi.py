@@ -83,3 +83,30 @@ def test_operator_asserts_mirror_the_reference(lib_path):
     with pytest.raises(AssertionError):
         ops.gemm_w4a4(torch.zeros(128, 64, dtype=torch.uint8), torch.zeros(128, 64, dtype=torch.uint8),
                       torch.zeros(8, 128), torch.zeros(8, 128))
+
+
+def test_header_is_plain_c_and_links(lib_path, tmp_path):
+    """include/svdq_b200.h must compile as C99 (it is the contract for cgo / JNI / FFI bindings) and a C
+    program must link against the library and call it without Python or PyTorch in the picture."""
+    import os
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler here")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "use_abi.c"
+    src.write_text(
+        '#include <string.h>\n#include "svdq_b200.h"\n'
+        "int main(void) {\n"
+        "  if (svdq_version() < 100) return 1;\n"
+        '  if (strcmp(svdq_status_string(SVDQ_OK), "ok") != 0) return 2;\n'
+        "  if (svdq_gemm_w4a4_supported(256, 128, 128, 16) != 1) return 3;\n"
+        "  if (svdq_lora_act16_elems(256, 32, SVDQ_DTYPE_BF16) != 3 * 256 * 32 + 16) return 4;\n"
+        "  return 0;\n}\n")
+    exe = tmp_path / "use_abi"
+    libdir = os.path.dirname(lib_path)
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(root, "include"),
+                    str(src), "-o", str(exe), "-L", libdir, "-l:" + os.path.basename(lib_path),
+                    "-Wl,-rpath," + libdir], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
