@@ -34,6 +34,9 @@
 //
 // A stage holds one 256-element K slab: A 128 x 128 B, B rows x 128 B (both
 // 128-byte swizzled, K-major, two E2M1 codes per byte) and their scale atoms.
+// The scale atoms are requested first and complete on a barrier of their own,
+// which is all the scale copiers wait for: a stage's scales are in tensor
+// memory by the time its operand tiles land.
 // The LoRA-up product reuses the very same ring: a slab of 64 rank elements of
 // lora_act (128 rows x 128 B) and lora_up (B rows x 128 B) has exactly the byte
 // footprint of a main slab, so it is ceil(R/64) more ring passes per output
@@ -85,7 +88,7 @@ struct Cfg {
   static constexpr int GROUPS_PER_WARP = BN / 128;                 // 64-column strips each epilogue warp handles per tile
   static constexpr int STORE_BUFS = 1;
   static constexpr int STORE_BYTES = EPI_WARPS * STORE_BUFS * STORE_BUF_BYTES;
-  static constexpr int TAIL_BYTES = 2048 /*affine*/ + 256 /*barriers*/;
+  static constexpr int TAIL_BYTES = 2048 /*affine*/ + 512 /*barriers*/;
   static constexpr int STAGES_RAW = (232448 - 1024 - STORE_BYTES - TAIL_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SFA_COLS = 16;                 // 4 k-blocks x 4 columns
@@ -100,7 +103,7 @@ struct Cfg {
   static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + STORE_BYTES + TAIL_BYTES;
   static_assert(ACC_STAGES * BN + SF_BUFS * SF_COLS <= TMEM_COLS, "tensor memory budget");
   static_assert(STAGES >= 3, "ring too shallow");
-  static_assert((2 * STAGES + 2 * ACC_STAGES + 2 * SF_BUFS) * 8 + 16 <= 256, "barrier block");
+  static_assert((3 * STAGES + 2 * ACC_STAGES + 2 * SF_BUFS) * 8 + 16 <= 512, "barrier block");
 };
 
 struct Params {
@@ -159,9 +162,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* tail = store_bufs + C::STORE_BYTES;
   float* affine = reinterpret_cast<float*>(tail);                 // [2][BN] : wcscales, bias of the current tile
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2048);
-  uint64_t* full = bars;                                          // [STAGES]     loads landed (leader CTA's copy is used)
+  uint64_t* full = bars;                                          // [STAGES]     A / B (or LoRA) operands landed (leader CTA's copy is used)
   uint64_t* empty = bars + C::STAGES;                             // [STAGES]     stage consumed by the MMAs (per CTA)
-  uint64_t* acc_full = bars + 2 * C::STAGES;                      // [ACC_STAGES] accumulator complete (per CTA)
+  uint64_t* full_sf = bars + 2 * C::STAGES;                       // [STAGES]     the stage's scale atoms landed (leader's copy)
+  uint64_t* acc_full = bars + 3 * C::STAGES;                      // [ACC_STAGES] accumulator complete (per CTA)
   uint64_t* acc_empty = acc_full + C::ACC_STAGES;                 // [ACC_STAGES] accumulator drained (leader's copy is used)
   uint64_t* sf_full = acc_empty + C::ACC_STAGES;                  // [SF_BUFS] scale buffer copied (leader CTA)
   uint64_t* sf_empty = sf_full + C::SF_BUFS;                      // [SF_BUFS] scale buffer consumed by the MMAs (leader CTA)
@@ -184,7 +188,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&full_sf[s], 1); }
     for (int a = 0; a < C::ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EPI_WARPS * CG); }
     for (int b = 0; b < C::SF_BUFS; ++b) { mbar_init(&sf_full[b], SF_WARPS); mbar_init(&sf_empty[b], 1); }
     fence_barrier_init();
@@ -245,20 +249,27 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // consecutive 512-byte rows of the swizzled scale buffer seen as a [blocks * K/64, 512 B] matrix;
         // a short last slab just fetches (and never uses) the rows that follow.  Every byte of a box
         // counts toward the barrier whether it was in bounds or not.
-        const uint32_t my_bytes = kt < kt_main ? C::STAGE_BYTES : A_BYTES + C::B_BYTES;
-        // the barrier that counts this CTA's bytes: its own for CG = 1, the leader's for a pair
+        // Two barriers per stage: the scale atoms (6 KB, requested first) complete on full_sf, the
+        // operand tiles on full.  The scale copiers work off full_sf, so a stage's scales are already in
+        // tensor memory when its operands land and the MMAs can start at once.  A LoRA slab has no
+        // scales; its full_sf is completed by a plain arrival so that both barriers flip once per slab.
+        constexpr uint32_t kSfBytes = SFA_BYTES + C::SFB_BYTES, kAbBytes = A_BYTES + C::B_BYTES;
+        // the barriers that count this CTA's bytes: its own for CG = 1, the leader's for a pair
         const uint32_t bar = (CG == 2) ? map_to_cta(smem_u32(&full[s]), 0) : smem_u32(&full[s]);
+        const uint32_t bar_sf = (CG == 2) ? map_to_cta(smem_u32(&full_sf[s]), 0) : smem_u32(&full_sf[s]);
         if (elect_one()) {
-          if (rank == 0) mbar_arrive_expect_tx(&full[s], my_bytes * CG);
           if (kt < kt_main) {
-            tma_load_2d_bar<CG>(st, &tmA, kt * 128, m0, bar);
-            tma_load_2d_bar<CG>(st + A_BYTES, &tmB, kt * 128, nrow0, bar);
-            tma_load_2d_bar<CG>(st + A_BYTES + C::B_BYTES, &tmSFA, 0, (mb * CG + rank) * k_groups4 + kt * 4, bar);
+            if (rank == 0) mbar_arrive_expect_tx(&full_sf[s], kSfBytes * CG);
+            tma_load_2d_bar<CG>(st + A_BYTES + C::B_BYTES, &tmSFA, 0, (mb * CG + rank) * k_groups4 + kt * 4, bar_sf);
 #pragma unroll
             for (int h = 0; h < BN / 128; ++h)
               tma_load_2d_bar<CG>(st + A_BYTES + C::B_BYTES + SFA_BYTES + h * 2048, &tmSFB, 0,
-                                  (nb * (BN / 128) + h) * k_groups4 + kt * 4, bar);
+                                  (nb * (BN / 128) + h) * k_groups4 + kt * 4, bar_sf);
+            if (rank == 0) mbar_arrive_expect_tx(&full[s], kAbBytes * CG);
+            tma_load_2d_bar<CG>(st, &tmA, kt * 128, m0, bar);
+            tma_load_2d_bar<CG>(st + A_BYTES, &tmB, kt * 128, nrow0, bar);
           } else {
+            if (rank == 0) { mbar_arrive(&full_sf[s]); mbar_arrive_expect_tx(&full[s], kAbBytes * CG); }
             const int lt = kt - kt_main;
             const int part = lt / lora_slabs, r0 = (lt % lora_slabs) * 64;
             if (la_fp16) {
@@ -342,7 +353,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // waiter that skipped ahead could get two ring revolutions in front of the producer, where the
           // parity of a barrier no longer tells the revolutions apart.
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
-          if (!uwait(&full[s], ph, ctx, kDevWaitFull, 0x20000 + it)) { ok = false; break; }
+          if (!uwait(&full_sf[s], ph, ctx, kDevWaitFull, 0x20000 + it)) { ok = false; break; }
           if (kt >= kt_main) continue;
           const uint32_t sb = sf_it % C::SF_BUFS;
           if (!uwait(&sf_empty[sb], ((sf_it / C::SF_BUFS) & 1) ^ 1, ctx, kDevWaitMisc, 0x20000 + it)) { ok = false; break; }
