@@ -331,9 +331,11 @@ def run_ours(args):
     e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
     g_tflops = flops / (g_us * 1e-6) / 1e12
     q_gbs = qbytes / (q_us * 1e-6) / 1e9
-    # tensor peak: the cuBLAS bf16 burst figure unless this run was held down by the power cap, in which
-    # case the sustained figure measured the same way (a seconds-long loop under the cap) is the fair one
-    capped = "sw_power_cap" in (clocks.get("reasons") or []) and peaks.get("bf16_tflops_sustained")
+    # tensor peak: the cuBLAS bf16 burst figure unless this run was held down by the power cap (reason seen
+    # and the median SM clock clearly below its maximum), in which case the sustained figure measured the
+    # same way (a seconds-long loop under the cap) is the fair one
+    capped = ("sw_power_cap" in (clocks.get("reasons") or []) and peaks.get("bf16_tflops_sustained")
+              and clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] < 0.97 * clocks["sm_max_mhz"])
     bf16_peak = peaks["bf16_tflops_sustained"] if capped else peaks["bf16_tflops"]
     nvfp4_peak = 4.0 * bf16_peak
     line = {
