@@ -401,7 +401,18 @@ def cpu_baseline(shape, args):
             "sample": f"{reps} passes over the first {rows} of {shape.M} rows (quantizer + GEMM oracle, numpy/BLAS), {dt:.2f} s each"}
 
 
+def _claim_stdout():
+    """Keep the real stdout for the one JSON line and send everything else that writes to file
+    descriptor 1 (library banners such as NCCL's version line, stray prints) to stderr."""
+    real = os.fdopen(os.dup(1), "w")
+    sys.stdout.flush()
+    os.dup2(2, 1)
+    sys.stdout = real
+    return real
+
+
 def main():
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
