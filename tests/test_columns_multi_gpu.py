@@ -1,5 +1,5 @@
-"""Column-sharded linear with the all-gather fused into the GEMM epilogue, on 2 GPUs (skipped with
-fewer): every rank's copy of the result must equal, bit for bit, what one GPU computes alone, and
+"""Column-sharded linear with the all-gather fused into the GEMM epilogue, on 2, 4 and 8 GPUs (each
+skipped on a machine with fewer): every rank's copy of the result must equal, bit for bit, what one GPU computes alone, and
 the NCCL all-gather form of the same sharding must agree too."""
 import os
 
@@ -34,7 +34,7 @@ def _worker(rank, world, port, dtype_name, q):
         wgt, wsc = ops.quantize_nvfp4_rows(w.to(dev), pad_size=1)
         y_one = ops.gemm_w4a4(act, wgt, asc, wsc, la, lu.to(dev), c.to(dev), b.to(dev), dtype)
 
-        col0, n = sharding.column_slab(N, world, rank, multiple=256)
+        col0, n = sharding.column_slab(N, world, rank, multiple=128)
         sl = slice(col0, col0 + n)
         lin = sharding.ColumnShardedLinear(M, N, dtype, wgt=wgt[sl].contiguous(), wscales=wsc[:, sl].contiguous(),
                                            lora_up=lu[sl].to(dev).contiguous(), wcscales=c[sl].to(dev).contiguous(),
@@ -61,11 +61,11 @@ def _worker(rank, world, port, dtype_name, q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("dtype_name", ["float16", "bfloat16"])
-def test_fused_all_gather_matches_single_gpu(dtype_name):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
-    world = 2
+def test_fused_all_gather_matches_single_gpu(dtype_name, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29600 + (os.getpid() % 300)
