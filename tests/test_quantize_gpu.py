@@ -210,3 +210,27 @@ def test_signed_zeros_and_negative_smooth(dtype, smooth_kind):
         sm = sm.to(dtype).cuda()
     _check(x.cuda(), ld.cuda(), sm, FUSED)
     _check(x.cuda(), ld.cuda(), sm, GENERIC)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_no_rows_and_strided_input(dtype):
+    """An input without rows gives empty outputs of the right shapes and types and launches nothing
+    that fails; a non-contiguous view of x is quantised like its contiguous copy."""
+    ops = _ops()
+    K, R = 128, 16
+    ld = torch.zeros(K, R, dtype=dtype).cuda()
+    sm = torch.ones(K, dtype=dtype).cuda()
+    act, ascales, lora = ops.quantize_w4a4_act_fuse_lora(torch.empty(0, K, dtype=dtype).cuda(), ld, sm, fp4=True)
+    torch.cuda.synchronize()
+    assert_device_clean()
+    assert tuple(act.shape) == (0, K // 2) and tuple(ascales.shape) == (K // 16, 0) and tuple(lora.shape) == (0, R)
+    assert act.dtype == torch.uint8 and ascales.dtype == torch.float8_e4m3fn and lora.dtype == torch.float32
+
+    x, ld, sm = _inputs(300, 512, 32, dtype, 77)
+    wide = torch.zeros(300, 1024, dtype=dtype).cuda()
+    wide[:, ::2] = x
+    a1, s1, l1 = ops.quantize_w4a4_act_fuse_lora(wide[:, ::2], ld, sm, fp4=True)
+    a2, s2, l2 = ops.quantize_w4a4_act_fuse_lora(x, ld, sm, fp4=True)
+    torch.cuda.synchronize()
+    assert_device_clean()
+    assert torch.equal(a1, a2) and torch.equal(s1.view(torch.uint8), s2.view(torch.uint8)) and torch.equal(l1, l2)
