@@ -47,8 +47,23 @@ def _peaks():
         with open(path) as f:
             p = json.load(f)
         return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
-                "source": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+                "sustained_mhz": (p.get("clocks_under_load") or {}).get("sm_mhz_median"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "sustained_mhz": 1300.0, "source": "fallback"}
+
+
+def _tensor_peak(peaks, clocks):
+    """bf16 peak to compare against, and a note.  The burst figure belongs to the maximum SM clock, the
+    sustained one to the clock the seconds-long loop settled at under the power cap.  A run that the
+    power cap held at a clock in between gets the figure interpolated at its own median clock, so that
+    a few per cent of clock never swing the denominator by the whole burst-sustained gap."""
+    burst, sus = peaks["bf16_tflops"], peaks.get("bf16_tflops_sustained")
+    f, fmax, fsus = clocks.get("sm_mhz"), clocks.get("sm_max_mhz"), peaks.get("sustained_mhz")
+    capped = "sw_power_cap" in (clocks.get("reasons") or [])
+    if not (capped and sus and f and fmax and fsus and fsus < fmax and f < 0.97 * fmax):
+        return burst, "burst"
+    t = min(1.0, max(0.0, (f - fsus) / (fmax - fsus)))
+    peak = sus + (burst - sus) * t
+    return peak, f"between sustained ({sus} at {fsus:.0f} MHz) and burst ({burst} at {fmax:.0f} MHz), at this run's {f:.0f} MHz under the power cap"
 
 
 class ClockSampler(threading.Thread):
@@ -331,12 +346,9 @@ def run_ours(args):
     e2e_value = world * flops / (e2e_ms * 1e-3) / 1e12
     g_tflops = flops / (g_us * 1e-6) / 1e12
     q_gbs = qbytes / (q_us * 1e-6) / 1e9
-    # tensor peak: the cuBLAS bf16 burst figure unless this run was held down by the power cap (reason seen
-    # and the median SM clock clearly below its maximum), in which case the sustained figure measured the
-    # same way (a seconds-long loop under the cap) is the fair one
-    capped = ("sw_power_cap" in (clocks.get("reasons") or []) and peaks.get("bf16_tflops_sustained")
-              and clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] < 0.97 * clocks["sm_max_mhz"])
-    bf16_peak = peaks["bf16_tflops_sustained"] if capped else peaks["bf16_tflops"]
+    # tensor peak: the cuBLAS bf16 burst figure, lowered towards the sustained one only as far as the
+    # power cap lowered this run's own median SM clock
+    bf16_peak, peak_kind = _tensor_peak(peaks, clocks)
     nvfp4_peak = 4.0 * bf16_peak
     line = {
         "metric": "w4a4_linear_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -352,8 +364,8 @@ def run_ours(args):
                      "frac": g_tflops / nvfp4_peak, "traffic": NCU_DRAM_BYTES.get(shape.name, {}).get("gemm_w4a4_kernel"),
                      "algorithmic_bytes": M_pad * K // 2 + N * K // 2 + (M_pad + N) * K // 16 + M_pad * N * 2 + (M_pad + N) * R * 2,
                      "kernel": "gemm_w4a4_kernel",
-                     "peak_note": f"4 x {peaks['source']} bf16 cuBLAS {'sustained (run was power-capped)' if capped else 'burst'} "
-                                  f"({bf16_peak} TF/s): no NVFP4 figure is measured on this pool; 4 is the nominal nvfp4:bf16 rate ratio"},
+                     "peak_note": f"4 x {peaks['source']} bf16 cuBLAS {peak_kind} "
+                                  f"({bf16_peak:.1f} TF/s): no NVFP4 figure is measured on this pool; 4 is the nominal nvfp4:bf16 rate ratio"},
         "roofline_quantizer": {"bound": "hbm", "achieved": q_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                                "frac": q_gbs / peaks["hbm_gbs"], "traffic": NCU_DRAM_BYTES.get(shape.name, {}).get("quantize_fused_kernel"),
                                "algorithmic_bytes": qbytes, "kernel": "quantize_fused_kernel",
