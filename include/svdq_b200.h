@@ -148,6 +148,26 @@ int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, co
                    void* y, int M, int N, int K, int R, int dtype, int variant, void* stream);
 
 /*
+ * svdq_gemm_w4a4 with a caller-owned workspace in device memory, for problems with few output tiles
+ * (a few hundred rows: the small-M shapes of GEMM_SHAPES in
+ * cute_kernels/gemm_w4a4/harness.py:17-24, where the reference's kernels leave most SMs idle).
+ * With variant 0 and a workspace of at least svdq_gemm_w4a4_workspace_bytes(M, N, K, R) bytes the
+ * library shares each 128 x 128 tile's K loop among several CTAs (split-K): each adds its part in
+ * fp32, parks it in the workspace, and the CTA that arrives last sums the parts in a fixed order
+ * and writes y, so results do not depend on timing.  variant 10000 * S + 128 forces S CTAs per tile.
+ * svdq_gemm_w4a4_workspace_bytes returns 0 where splitting does not apply; then (or with a NULL or
+ * smaller workspace) the call is svdq_gemm_w4a4.
+ * The first 1024 bytes of the workspace are ticket counters: zero them once before the first call;
+ * every call leaves them zero.  Calls that share a workspace must not overlap in time (same stream,
+ * or ordered by events); after a call whose bounded wait expired (svdq_device_status != 0) zero it again.
+ */
+unsigned long long svdq_gemm_w4a4_workspace_bytes(int M, int N, int K, int R);
+int svdq_gemm_w4a4_ws(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                      const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales, const void* bias,
+                      void* y, int M, int N, int K, int R, int dtype, int variant, void* workspace,
+                      unsigned long long workspace_bytes, void* stream);
+
+/*
  * Column-sharded (tensor-parallel) form of svdq_gemm_w4a4, one call per GPU: this GPU holds rows
  * [col0, col0 + N) of wgt / wscales / lora_up / wcscales / bias and computes those columns of the
  * [M, N_total] result.  Every finished 32 x 64 strip is written into y_full (this GPU's copy of the

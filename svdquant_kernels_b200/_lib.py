@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_longlong, c_void_p, POINTER, c_float, c_uint
+from ctypes import c_char_p, c_int, c_longlong, c_ulonglong, c_void_p, POINTER, c_float, c_uint
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG_DIR, "libsvdq_b200.so")
@@ -31,6 +31,8 @@ SIGNATURES = {
     "svdq_cast_lora_act": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "svdq_lora_up_to_f16": (c_int, [c_void_p, c_void_p, c_longlong]),
     "svdq_gemm_w4a4": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p]),
+    "svdq_gemm_w4a4_workspace_bytes": (c_ulonglong, [c_int, c_int, c_int, c_int]),
+    "svdq_gemm_w4a4_ws": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p, c_ulonglong, c_void_p]),
     "svdq_gemm_w4a4_columns": (c_int, [c_void_p] * 10 + [POINTER(c_void_p)] + [c_int] * 9 + [c_void_p]),
     "svdq_gemm_w4a4_supported": (c_int, [c_int, c_int, c_int, c_int]),
     "svdq_device_status": (c_int, [POINTER(c_uint)]),

@@ -136,9 +136,10 @@ int svdq_quantizer_max_active_clusters(int R, int k_split, int dtype) {
 
 int svdq_gemm_w4a4_supported(int M, int N, int K, int R) { return gemm_supported(M, N, K, R) ? 1 : 0; }
 
-int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
-                   const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
-                   const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant, void* stream) {
+static int gemm_entry(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                      const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
+                      const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant, void* workspace,
+                      size_t workspace_bytes, void* stream) {
   if (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16) return SVDQ_ERR_DTYPE;
   if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
   if (act == nullptr || wgt == nullptr || ascales_swz == nullptr || wscales_swz == nullptr || y == nullptr)
@@ -147,10 +148,32 @@ int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, co
   if (R > 0 && lora_act16 == nullptr) return SVDQ_ERR_NULL;
   if (lora_act16 == nullptr) R = 0;
   if (!aligned16(act) || !aligned16(wgt) || !aligned16(ascales_swz) || !aligned16(wscales_swz) ||
-      !aligned16(lora_act16) || !aligned16(lora_up) || !aligned16(lora_up_f16) || !aligned16(y))
+      !aligned16(lora_act16) || !aligned16(lora_up) || !aligned16(lora_up_f16) || !aligned16(y) || !aligned16(workspace))
     return SVDQ_ERR_ALIGN;
+  GemmTp extra;
+  extra.ws = workspace;
+  extra.ws_bytes = workspace != nullptr ? workspace_bytes : 0;
   return launch_gemm_w4a4(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N,
-                          K, R, dtype, variant, GemmTp(), static_cast<cudaStream_t>(stream));
+                          K, R, dtype, variant, extra, static_cast<cudaStream_t>(stream));
+}
+
+int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                   const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
+                   const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant, void* stream) {
+  return gemm_entry(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R,
+                    dtype, variant, nullptr, 0, stream);
+}
+
+unsigned long long svdq_gemm_w4a4_workspace_bytes(int M, int N, int K, int R) {
+  return static_cast<unsigned long long>(gemm_split_workspace_bytes(M, N, K, R));
+}
+
+int svdq_gemm_w4a4_ws(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                      const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
+                      const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant, void* workspace,
+                      unsigned long long workspace_bytes, void* stream) {
+  return gemm_entry(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R,
+                    dtype, variant, workspace, static_cast<size_t>(workspace_bytes), stream);
 }
 
 int svdq_gemm_w4a4_columns(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
@@ -213,6 +236,8 @@ struct svdq_linear_plan {
   PlanSlot slot[kPlanSlots];
   unsigned long long submitted;
   void *wgt, *wscales_swz, *lora_down, *lora_up, *lora_up_f16, *smooth, *smooth_table, *wc, *bias;  // resident weights
+  void* split_ws;                                                // split-K workspace of the GEMM (few-row calls, long K), or null
+  size_t split_ws_bytes;
 };
 
 static bool is_pinned_host(const void* ptr) {
@@ -283,6 +308,12 @@ int svdq_linear_plan_create(svdq_linear_plan** out, int max_M, int K, int N, int
   }
   if (rc == SVDQ_OK) rc = dev_upload(&p->wc, wcscales_host, static_cast<size_t>(N) * 2, st);
   if (rc == SVDQ_OK) rc = dev_upload(&p->bias, bias_host, static_cast<size_t>(N) * 2, st);
+  if (rc == SVDQ_OK && gemm_split_plan(256, N, K, R) > 1) {
+    // a call with few rows may take the split-K form: tiles x splits never exceeds the SM count
+    p->split_ws_bytes = kSplitTicketBytes + static_cast<size_t>(sm_count()) * (128 * 128 * 4);
+    if (cudaMalloc(&p->split_ws, p->split_ws_bytes) != cudaSuccess ||
+        cudaMemsetAsync(p->split_ws, 0, kSplitTicketBytes, st) != cudaSuccess) rc = SVDQ_ERR_CUDA;
+  }
   if (rc == SVDQ_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = SVDQ_ERR_CUDA;
   if (wscales_dev != nullptr) cudaFree(wscales_dev);
   if (rc != SVDQ_OK) {
@@ -331,10 +362,9 @@ int svdq_linear_plan_submit(svdq_linear_plan* p, const void* x_host, void* y_hos
                                         q.ascales_swz, q.lora_act16, M, p->K, p->R, M_pad, p->dtype, SVDQ_QUANT_AUTO,
                                         p->s_run);
   if (rc != SVDQ_OK) return rc;
-  rc = svdq_gemm_w4a4(q.act, p->wgt, q.ascales_swz, p->wscales_swz, p->R > 0 ? q.lora_act16 : nullptr,
-                      p->R > 0 ? p->lora_up : nullptr, p->R > 0 ? p->lora_up_f16 : nullptr, p->wc, p->bias, q.y, M_pad, p->N,
-                      p->K, p->R, p->dtype, 0,
-                      p->s_run);
+  rc = svdq_gemm_w4a4_ws(q.act, p->wgt, q.ascales_swz, p->wscales_swz, p->R > 0 ? q.lora_act16 : nullptr,
+                         p->R > 0 ? p->lora_up : nullptr, p->R > 0 ? p->lora_up_f16 : nullptr, p->wc, p->bias, q.y, M_pad,
+                         p->N, p->K, p->R, p->dtype, 0, p->split_ws, p->split_ws_bytes, p->s_run);
   if (rc != SVDQ_OK) return rc;
   bad = bad || cudaEventRecord(q.computed, p->s_run) != cudaSuccess;
   // y copy
@@ -379,7 +409,8 @@ void svdq_linear_plan_destroy(svdq_linear_plan* p) {
     if (q.computed != nullptr) cudaEventDestroy(q.computed);
     if (q.y_done != nullptr) cudaEventDestroy(q.y_done);
   }
-  void* dev[] = {p->wgt, p->wscales_swz, p->lora_down, p->lora_up, p->lora_up_f16, p->smooth, p->smooth_table, p->wc, p->bias};
+  void* dev[] = {p->wgt, p->wscales_swz, p->lora_down, p->lora_up, p->lora_up_f16, p->smooth, p->smooth_table, p->wc, p->bias,
+                 p->split_ws};
   for (void* d : dev)
     if (d != nullptr) cudaFree(d);
   if (p->s_in != nullptr) cudaStreamDestroy(p->s_in);

@@ -54,6 +54,14 @@
 // Column-sharded form (n_peers > 0): the launch fills N columns of a wider result
 // that every GPU holds in full; each finished strip is also written, with plain
 // 16-byte stores from the staging buffer, into the peers' copies over NVLink.
+//
+// Split-K form (SK = true, one CTA per 128 x 128 tile part): for problems with few tiles and a
+// long K, S CTAs share a tile's slabs.  Each parks its fp32 partial tile in a caller-owned
+// workspace (thread t writes float4 j at [j][t], so every access is a whole line per warp and a
+// thread later reads back exactly the places its namesakes wrote), fences, and draws a ticket
+// from the tile's counter; the CTA that draws ticket S - 1 adds the S partials in split order -
+// the result does not depend on who finished first - runs the epilogue and zeroes the counter.
+// No CTA waits for another, so nothing depends on the CTAs of a tile running together.
 #include "nvfp4_math.cuh"
 #include "sm100.cuh"
 #include "svdq_internal.h"
@@ -118,6 +126,13 @@ struct Params {
   // from the staging buffer, into the same place of every peer's matrix (peer-mapped memory).
   int col0, y_ld, n_peers;
   void* y_peer[7];
+  // Split-K form (SK kernels only): a tile's slabs are shared by `splits` CTAs; each writes its fp32
+  // partial tile to ws_partials[(tile * splits + split) * BM * BN], takes a ticket from
+  // ws_tickets[tile], and the CTA that draws the last ticket adds the partials in split order, runs
+  // the epilogue and puts the ticket counter back to zero.
+  int splits;
+  float4* ws_partials;
+  unsigned int* ws_tickets;
 };
 
 __device__ __forceinline__ uint32_t pack2(__half a, __half b) {
@@ -144,7 +159,7 @@ template <typename T> __device__ __forceinline__ float as_f32(T v);
 template <> __device__ __forceinline__ float as_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float as_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-template <int CG, int BN, typename OutT>
+template <int CG, int BN, typename OutT, bool SK = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmLA, const __grid_constant__ CUtensorMap tmLU,
@@ -171,6 +186,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* sf_empty = sf_full + C::SF_BUFS;                      // [SF_BUFS] scale buffer consumed by the MMAs (leader CTA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + C::SF_BUFS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile uint32_t* sk_ticket = tmem_slot + 2;                   // split-K: the ticket this CTA drew for its tile
   const WaitCtx ctx{abort_flag};
   // bounded wait whose verdict is the same in all lanes of the calling (converged) warp
   auto uwait = [&](uint64_t* bar, uint32_t parity, const WaitCtx& c, unsigned int code, unsigned int tag) -> bool {
@@ -229,19 +245,30 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto lora_parts = [&](bool fp16_pass) -> int { return (kBf16 && !fp16_pass) ? 2 : 1; };
   const int total_tiles = p.tiles_m * p.tiles_n;
   const int k_groups4 = p.K / 64;            // scale atoms along K
+  // Work items: tiles, or (tile, split) pairs numbered tile-major so that the CTAs sharing a tile run
+  // at the same time.  Split i of a tile with n slabs (LoRA slabs included, at the end) takes slabs
+  // [i n / S, (i + 1) n / S).
+  const int S = SK ? p.splits : 1;
+  const int total_work = total_tiles * S;
+  auto slab_range = [&](int split, int kt_all, int& lo, int& hi) {
+    if (SK) { lo = split * kt_all / S; hi = (split + 1) * kt_all / S; } else { lo = 0; hi = kt_all; }
+  };
 
   if (warp == EPI_WARPS) {
     // ------------------------------ producer (both CTAs) ------------------------------
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+    for (int w = pair; w < total_work && ok; w += num_pairs) {
+      const int tile = SK ? w / S : w, split = SK ? w - tile * S : 0;
       const int mb = tile % p.tiles_m, nb = tile / p.tiles_m;
       const int m0 = (mb * CG + rank) * BM;
       const int n0 = nb * BN;
       const int nrow0 = n0 + rank * C::B_ROWS;
       const bool la_fp16 = lora_fp16(mb);
       const int kt_all = kt_main + lora_parts(la_fp16) * lora_slabs;
-      for (int kt = 0; kt < kt_all; ++kt, ++it) {
+      int kt_lo, kt_hi;
+      slab_range(split, kt_all, kt_lo, kt_hi);
+      for (int kt = kt_lo; kt < kt_hi; ++kt, ++it) {
         const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
         if (!uwait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, it)) { ok = false; break; }
         uint8_t* st = smem + s * C::STAGE_BYTES;
@@ -294,7 +321,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint16_t kMask = (CG == 2) ? 3 : 1;
       uint32_t it = 0, tcount = 0, sf_it = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++tcount) {
+      for (int w = pair; w < total_work && ok; w += num_pairs, ++tcount) {
+        const int tile = SK ? w / S : w, split = SK ? w - tile * S : 0;
         const uint32_t as = tcount % C::ACC_STAGES, aph = (tcount / C::ACC_STAGES) & 1;
         if (!uwait(&acc_empty[as], aph ^ 1, ctx, kDevWaitAccFree, tcount)) { ok = false; break; }
         tc_fence_after_sync();
@@ -302,7 +330,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool la_fp16 = lora_fp16(tile % p.tiles_m);
         const int kt_all = kt_main + lora_parts(la_fp16) * lora_slabs;
         const uint32_t idesc_lora = la_fp16 ? kIdescLoraF16 : kIdescLora;
-        for (int kt = 0; kt < kt_all; ++kt, ++it) {
+        int kt_lo, kt_hi;
+        slab_range(split, kt_all, kt_lo, kt_hi);
+        for (int kt = kt_lo; kt < kt_hi; ++kt, ++it) {
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
           if (!uwait(&full[s], ph, ctx, kDevWaitFull, it)) { ok = false; break; }
           const bool main_slab = kt < kt_main;
@@ -321,17 +351,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 4; ++j)
                 if (j < nkb)
                   mma_nvfp4<CG>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
-                                kIdescMain, tsfa + j * 4, tsfb + j * (BN / 32), (kt | j) != 0 ? 1u : 0u);
+                                kIdescMain, tsfa + j * 4, tsfb + j * (BN / 32), ((kt - kt_lo) | j) != 0 ? 1u : 0u);
               tc_commit_local<CG>(&sf_empty[sb]);   // scale buffer reusable once these MMAs are done
             } else {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
                 if (j < nkb)
                   mma_f16<CG>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
-                              idesc_lora, (kt | j) != 0 ? 1u : 0u);
+                              idesc_lora, ((kt - kt_lo) | j) != 0 ? 1u : 0u);
             }
             tc_commit_mask<CG>(&empty[s], kMask);          // stage reusable (in both CTAs) once these MMAs have read it
-            if (kt == kt_all - 1) tc_commit_mask<CG>(&acc_full[as], kMask);   // accumulator complete
+            if (kt == kt_hi - 1) tc_commit_mask<CG>(&acc_full[as], kMask);    // accumulator complete
           }
           __syncwarp();
           if (main_slab) ++sf_it;
@@ -346,9 +376,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int jlo = (warp - (EPI_WARPS + 2)) * (4 / SF_WARPS);            // this warp's k-blocks: jlo, jlo + 1
       uint32_t it = 0, sf_it = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+      for (int w = pair; w < total_work && ok; w += num_pairs) {
+        const int tile = SK ? w / S : w, split = SK ? w - tile * S : 0;
         const int kt_all = kt_main + lora_parts(lora_fp16(tile % p.tiles_m)) * lora_slabs;
-        for (int kt = 0; kt < kt_all; ++kt, ++it) {
+        int kt_lo, kt_hi;
+        slab_range(split, kt_all, kt_lo, kt_hi);
+        for (int kt = kt_lo; kt < kt_hi; ++kt, ++it) {
           // Every slab's barrier is waited on in order, LoRA slabs (which carry no scales) included: a
           // waiter that skipped ahead could get two ring revolutions in front of the producer, where the
           // parity of a barrier no longer tells the revolutions apart.
@@ -390,7 +423,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t swz = static_cast<uint32_t>(lane & 7);
     uint32_t tcount = 0, nstore = 0;
     bool ok = true;
-    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++tcount) {
+    for (int w = pair; w < total_work && ok; w += num_pairs, ++tcount) {
+      const int tile = SK ? w / S : w, split = SK ? w - tile * S : 0;
       const int mb = tile % p.tiles_m, nb = tile / p.tiles_m;
       const int m0 = (mb * CG + rank) * BM, n0 = nb * BN;
       const uint32_t as = tcount % C::ACC_STAGES, aph = (tcount / C::ACC_STAGES) & 1;
@@ -417,6 +451,62 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (lane == 0) {
         if constexpr (CG == 2) mbar_arrive_cluster(&acc_empty[as], 0); else mbar_arrive(&acc_empty[as]);
       }
+      bool finish = true;                       // this CTA writes the tile's rows of y
+      if constexpr (SK) {
+        if (S > 1) {
+          // Each thread parks its 16 x GROUPS_PER_WARP float4s at [j][thread] of the CTA's partial tile
+          // (consecutive threads, consecutive 16 bytes) and later reads the same places of the other
+          // partials, so no thread ever needs another thread's accumulator values.
+          constexpr int kVec = C::GROUPS_PER_WARP * 16;
+          constexpr int kTileVec = BM * BN / 4;
+          const int tid = threadIdx.x;
+          float4* mine = p.ws_partials + static_cast<size_t>(tile * S + split) * kTileVec;
+          const uint32_t* vf = &v[0][0][0];
+#pragma unroll
+          for (int j = 0; j < kVec; ++j)
+            __stcg(mine + j * (EPI_WARPS * 32) + tid,
+                   make_float4(__uint_as_float(vf[4 * j]), __uint_as_float(vf[4 * j + 1]), __uint_as_float(vf[4 * j + 2]),
+                               __uint_as_float(vf[4 * j + 3])));
+          __threadfence();
+          asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+          if (tid == 0) *sk_ticket = atomicAdd(p.ws_tickets + tile, 1u);
+          asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+          finish = *sk_ticket == static_cast<uint32_t>(S - 1);
+          if (finish) {
+            __threadfence();
+            // Partial sp is added as a whole before partial sp + 1 is looked at: one round trip to L2
+            // per partial with all of a thread's loads in flight together, and the same order of
+            // additions whatever order the CTAs finished in.
+            const float4* first = p.ws_partials + static_cast<size_t>(tile * S) * kTileVec + tid;
+            uint32_t* vw = &v[0][0][0];
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) {
+              const float4 t = __ldcg(first + j * (EPI_WARPS * 32));
+              vw[4 * j] = __float_as_uint(t.x); vw[4 * j + 1] = __float_as_uint(t.y);
+              vw[4 * j + 2] = __float_as_uint(t.z); vw[4 * j + 3] = __float_as_uint(t.w);
+            }
+#pragma unroll 1
+            for (int sp = 1; sp < S; ++sp) {
+              const float4* part = first + static_cast<size_t>(sp) * kTileVec;
+#pragma unroll
+              for (int h = 0; h < kVec; h += 8) {
+                float4 t[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t[j] = __ldcg(part + (h + j) * (EPI_WARPS * 32));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  vw[4 * (h + j)] = __float_as_uint(__uint_as_float(vw[4 * (h + j)]) + t[j].x);
+                  vw[4 * (h + j) + 1] = __float_as_uint(__uint_as_float(vw[4 * (h + j) + 1]) + t[j].y);
+                  vw[4 * (h + j) + 2] = __float_as_uint(__uint_as_float(vw[4 * (h + j) + 2]) + t[j].z);
+                  vw[4 * (h + j) + 3] = __float_as_uint(__uint_as_float(vw[4 * (h + j) + 3]) + t[j].w);
+                }
+              }
+            }
+            if (tid == 0) p.ws_tickets[tile] = 0u;      // every split has drawn its ticket: ready for the next launch
+          }
+        }
+      }
+      if (finish) {
 #pragma unroll
       for (int g = 0; g < C::GROUPS_PER_WARP; ++g, ++nstore) {
         uint8_t* buf = my_bufs + (nstore % C::STORE_BUFS) * STORE_BUF_BYTES;
@@ -478,6 +568,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
+      }
       // affine[] may be overwritten after this barrier; it also makes the eight warps agree on whether to go on
       uint32_t any_failed;
       asm volatile(
@@ -512,10 +603,10 @@ bool gemm_supported(int M, int N, int K, int R) {
   return M > 0 && N > 0 && K > 0 && M % 128 == 0 && N % 128 == 0 && K % 64 == 0 && R >= 0 && R % 16 == 0;
 }
 
-template <int CG, int BN, typename OutT>
+template <int CG, int BN, typename OutT, bool SK = false>
 static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, const void* sfb, const void* la,
                          const void* lu, const void* lu_f16, const void* wc, const void* bias, void* y, int M, int N,
-                         int K, int R, const GemmTp& tp, cudaStream_t stream) {
+                         int K, int R, const GemmTp& tp, cudaStream_t stream, int splits = 1) {
   using C = gemm::Cfg<CG, BN>;
   constexpr bool kBf16 = std::is_same<OutT, __nv_bfloat16>::value;
   CUtensorMap tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, tmLAf, tmLUf;
@@ -550,7 +641,10 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   p.tiles_m = M / (gemm::BM * CG); p.tiles_n = N / BN;
   p.col0 = tp.y_ld > 0 ? tp.col0 : 0; p.y_ld = y_ld; p.n_peers = tp.n_peers;
   for (int d = 0; d < 7; ++d) p.y_peer[d] = d < tp.n_peers ? tp.y_peer[d] : nullptr;
-  auto kern = gemm::gemm_w4a4_kernel<CG, BN, OutT>;
+  p.splits = SK ? splits : 1;
+  p.ws_tickets = static_cast<unsigned int*>(tp.ws);
+  p.ws_partials = tp.ws != nullptr ? reinterpret_cast<float4*>(static_cast<uint8_t*>(tp.ws) + kSplitTicketBytes) : nullptr;
+  auto kern = gemm::gemm_w4a4_kernel<CG, BN, OutT, SK>;
   // the attribute is per device: remember which devices of this process have it
   static bool configured[64] = {};
   int dev = 0;
@@ -559,7 +653,7 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return SVDQ_ERR_LAUNCH;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  const int tiles = p.tiles_m * p.tiles_n;
+  const int tiles = p.tiles_m * p.tiles_n * p.splits;
   const int max_pairs = sm_count() / CG;
   const int pairs = tiles < max_pairs ? tiles : max_pairs;
   cudaLaunchConfig_t cfg = {};
@@ -588,7 +682,33 @@ static int launch_gemm_dt(int cg, int bn, const void* act, const void* wgt, cons
   return launch_gemm_t<1, 128, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
 }
 
-// variant: 0 = choose; 128 / 256 = one CTA per tile with that N tile; 2128 / 2256 = CTA pairs (256-row tiles)
+// Split-K plan for a problem with few tiles: 128 x 128 tiles, each tile's slabs shared by S CTAs that
+// all run at once (tiles * S <= SMs).  One CTA streams a tile's slabs at about 0.3 us each however
+// few tiles there are (32 KB per slab through one SM's load path), so with a few dozen tiles most
+// SMs idle and the run time is one tile's K loop.  Splitting costs about 3.3 us (partials to L2, a
+// fence, the ticket, one read per partial), which the shorter loops repay from about 24 slabs on
+// (measured, 256 rows x 3072 columns: K = 3840 9.1 -> 10.0 us, K = 10240 16.1 -> 12.7 us,
+// K = 15360 22.6 -> 17.7 us).  Returns S (1 = no split).
+int gemm_split_plan(int M, int N, int K, int R) {
+  if (!gemm_supported(M, N, K, R)) return 1;
+  const long long tiles = static_cast<long long>(M / 128) * (N / 128);
+  const int slabs = (K + gemm::BK - 1) / gemm::BK;
+  const int sms = sm_count();
+  if (tiles * 2 > sms || tiles > kSplitMaxTiles || slabs < 24) return 1;
+  int s = static_cast<int>(sms / tiles);
+  if (s > 4) s = 4;
+  if (s > slabs / 6) s = slabs / 6;               // at least six slabs per split
+  return s < 2 ? 1 : s;
+}
+
+size_t gemm_split_workspace_bytes(int M, int N, int K, int R) {
+  const int s = gemm_split_plan(M, N, K, R);
+  if (s < 2) return 0;
+  return kSplitTicketBytes + static_cast<size_t>(M / 128) * (N / 128) * s * (128 * 128 * 4);
+}
+
+// variant: 0 = choose; 128 / 256 = one CTA per tile with that N tile; 2128 / 2256 = CTA pairs (256-row tiles);
+// 10000 * S + 128 = split-K with S CTAs per 128 x 128 tile (needs the workspace)
 int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
                      const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
                      const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant,
@@ -598,6 +718,28 @@ int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, 
   if (tp.y_ld > 0 && (tp.col0 < 0 || tp.col0 % 64 != 0 || tp.col0 + N > tp.y_ld || tp.y_ld % 8 != 0)) return SVDQ_ERR_SHAPE;
   if (tp.y_ld <= 0 && tp.n_peers > 0) return SVDQ_ERR_SHAPE;
   int cg, bn;
+  if (variant == 0 || variant >= 10000) {
+    // split-K: planned (variant 0, plain form, workspace large enough) or forced by the caller
+    int s = 1;
+    if (variant == 0 && tp.y_ld <= 0 && tp.ws != nullptr) {
+      s = gemm_split_plan(M, N, K, R);
+      if (s >= 2 && tp.ws_bytes < gemm_split_workspace_bytes(M, N, K, R)) s = 1;
+    } else if (variant >= 10000) {
+      s = variant / 10000;
+      const long long tiles = static_cast<long long>(M / 128) * (N / 128);
+      if (variant % 10000 != 128 || s < 2 || s > kSplitMax || tiles > kSplitMaxTiles || tp.ws == nullptr || tp.y_ld > 0 ||
+          s > (K + gemm::BK - 1) / gemm::BK || tiles * s > sm_count() ||
+          tp.ws_bytes < kSplitTicketBytes + static_cast<size_t>(tiles) * s * (128 * 128 * 4))
+        return SVDQ_ERR_UNSUPPORTED;
+    }
+    if (s >= 2) {
+      if (dtype == SVDQ_DTYPE_F16)
+        return launch_gemm_t<1, 128, __half, true>(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, nullptr, wcscales, bias, y, M, N, K, R, tp, stream, s);
+      if (dtype == SVDQ_DTYPE_BF16)
+        return launch_gemm_t<1, 128, __nv_bfloat16, true>(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R, tp, stream, s);
+      return SVDQ_ERR_DTYPE;
+    }
+  }
   if (variant == 0) {
     // Pick the tile shape with the least estimated time: waves of tiles over the SMs (or SM pairs)
     // times the measured relative time of one tile (a 128-column tile takes 0.72 of a 256-column

@@ -33,7 +33,15 @@ bool gemm_supported(int M, int N, int K, int R);
 struct GemmTp {
   int col0 = 0, y_ld = 0, n_peers = 0;
   void* y_peer[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  // split-K workspace (plain form only): ticket counters (zero between launches), then fp32 partial tiles
+  void* ws = nullptr;
+  size_t ws_bytes = 0;
 };
+constexpr size_t kSplitTicketBytes = 1024;     // 256 ticket counters
+constexpr int kSplitMaxTiles = 74;             // split-K is for problems with at most this many 128 x 128 tiles
+constexpr int kSplitMax = 6;                   // CTAs per tile at most
+int gemm_split_plan(int M, int N, int K, int R);
+size_t gemm_split_workspace_bytes(int M, int N, int K, int R);
 int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
                      const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
                      const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant,

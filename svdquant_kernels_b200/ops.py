@@ -221,8 +221,13 @@ def gemm_w4a4(
     tiler_mn: Optional[Tuple[int, int]] = None,
     lora_schedule: str = "interleave",
     _columns: Optional[Tuple[torch.Tensor, list, int]] = None,
+    _splits: Optional[int] = None,
 ) -> torch.Tensor:
-    """`_columns = (y_full, peer_ptrs, col0)` selects the column-sharded form (svdq_gemm_w4a4_columns):
+    """Problems with few output tiles (a few hundred rows) take the split-K form (svdq_gemm_w4a4_ws) with
+    a workspace cached per device and stream; `_splits = S` forces S CTAs per 128 x 128 tile, `_splits = 1`
+    forbids splitting.
+
+    `_columns = (y_full, peer_ptrs, col0)` selects the column-sharded form (svdq_gemm_w4a4_columns):
     the `[M, N]` result of this call goes into columns `[col0, col0 + N)` of the local `[M, N_total]`
     tensor `y_full` and of the peers' copies at the raw device pointers `peer_ptrs`; `y_full` is
     returned.  See `sharding.linear_columns_fused` for the ordering the caller owes."""
@@ -293,11 +298,37 @@ def gemm_w4a4(
         _lib.check(rc, "gemm_w4a4_columns")
         return y_full
     y = torch.empty((M, N), dtype=out_dtype, device=dev)
+    ws = None
+    if _splits is not None and _splits > 1:
+        variant = 10000 * _splits + 128
+        ws = _split_workspace(dev, 1024 + (M // 128) * (N // 128) * _splits * 65536)
+    elif variant == 0 and _splits is None:
+        need = int(lib.svdq_gemm_w4a4_workspace_bytes(M, N, K, R))
+        if need > 0:
+            ws = _split_workspace(dev, need)
     with torch.cuda.device(dev):
-        rc = lib.svdq_gemm_w4a4(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc), _ptr(b), _ptr(y),
-                                M, N, K, R, _DT[out_dtype], variant, _stream(dev))
+        if ws is not None:
+            rc = lib.svdq_gemm_w4a4_ws(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc), _ptr(b),
+                                       _ptr(y), M, N, K, R, _DT[out_dtype], variant, _ptr(ws), ws.numel(), _stream(dev))
+        else:
+            rc = lib.svdq_gemm_w4a4(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc), _ptr(b),
+                                    _ptr(y), M, N, K, R, _DT[out_dtype], variant, _stream(dev))
     _lib.check(rc, "gemm_w4a4")
     return y
+
+
+_SPLIT_WS: dict = {}
+
+
+def _split_workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """Split-K workspace of the current stream of `dev` (zeroed when made; every call leaves its ticket
+    counters zero).  One per stream, because calls that share a workspace must not overlap."""
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev))
+    ws = _SPLIT_WS.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 10 << 20), dtype=torch.uint8, device=dev)
+        _SPLIT_WS[key] = ws
+    return ws
 
 
 launch_v2 = gemm_w4a4   # the reference's name for the same entry point

@@ -19,7 +19,7 @@ def _ops():
     return ops
 
 
-def _case(M, K, N, R, dtype, seed, wc=True, bias=True, tiler=None, act="gauss"):
+def _case(M, K, N, R, dtype, seed, wc=True, bias=True, tiler=None, act="gauss", splits=None, repeat=1):
     ops = _ops()
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(M, K, generator=g)
@@ -37,8 +37,10 @@ def _case(M, K, N, R, dtype, seed, wc=True, bias=True, tiler=None, act="gauss"):
     act_t, asc, la = ops.quantize_w4a4_act_fuse_lora(x.to(dev), ld.to(dev), sm.to(dev))
     wgt, wsc = ops.quantize_nvfp4_rows(w.to(dev), pad_size=1)
     has_lora = R > 0
-    y = ops.gemm_w4a4(act_t, wgt, asc, wsc, la if has_lora else None, lu.to(dev) if has_lora else None,
-                      None if c is None else c.to(dev), None if b is None else b.to(dev), dtype, tiler_mn=tiler)
+    for _ in range(repeat):
+        y = ops.gemm_w4a4(act_t, wgt, asc, wsc, la if has_lora else None, lu.to(dev) if has_lora else None,
+                          None if c is None else c.to(dev), None if b is None else b.to(dev), dtype, tiler_mn=tiler,
+                          _splits=splits)
     torch.cuda.synchronize()
     assert_device_clean()
     y_bits, _ = oracle_gemm(u8(act_t), u8(wgt), u8(asc), u8(wsc), la.cpu().numpy() if has_lora else None,
@@ -204,3 +206,36 @@ def test_back_to_back_steps_keep_their_results():
         for i, (a, c) in enumerate(zip(alone, chained)):
             assert torch.equal(a, c), f"repetition {rep}, step {i}"
     assert_device_clean()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N,R,splits", [(256, 7680, 3072, 128, None), (256, 3840, 3072, 128, 2), (256, 3840, 3072, 128, 3),
+                                            (128, 1024, 256, 0, 4), (128, 2560, 512, 32, 6), (384, 704, 1280, 256, 3),
+                                            (128, 10240, 3072, 32, None), (512, 15360, 1024, 64, None)])
+def test_split_k(M, K, N, R, splits, dtype):
+    """Few output tiles: a tile's K loop is shared by several CTAs whose fp32 partial tiles are summed
+    in a fixed order by the last one to arrive.  Chosen by the library (None) or forced; twice in a
+    row and with changing split counts on the same workspace (the ticket counters return to zero)."""
+    ops = _ops()
+    if splits is None:
+        assert int(ops._lib.load().svdq_gemm_w4a4_workspace_bytes(M, N, K, R)) > 0, "this shape should split"
+    assert _case(M, K, N, R, dtype, seed=M + K, splits=splits, repeat=2) <= TOL
+    assert _case(M, K, N, R, dtype, seed=M + K + 1, splits=2, repeat=1) <= TOL
+    assert _case(M, K, N, R, dtype, seed=M + K + 2, splits=1) <= TOL
+
+
+def test_split_k_is_deterministic():
+    """The order of summation is fixed by the split index, not by arrival: ten runs, one result."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(8)
+    M, K, N, R, dtype = 256, 3840, 1536, 64, torch.float16
+    x = torch.randn(M, K, generator=g).to(dtype).cuda()
+    ld = (torch.randn(K, R, generator=g) / K ** 0.5).to(dtype).cuda()
+    lu = (torch.randn(N, R, generator=g) * 0.01).to(dtype).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.02).cuda()
+    act, asc, la = ops.quantize_w4a4_act_fuse_lora(x, ld, None)
+    wgt, wsc = ops.quantize_nvfp4_rows(w, pad_size=1)
+    ys = [ops.gemm_w4a4(act, wgt, asc, wsc, la, lu, None, None, dtype, _splits=4) for _ in range(10)]
+    torch.cuda.synchronize()
+    assert_device_clean()
+    assert all(torch.equal(ys[0], y) for y in ys[1:])

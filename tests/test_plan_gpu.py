@@ -82,3 +82,19 @@ def test_plan_rejects_bad_calls():
             plan.forward_host(x, y)          # more rows than the plan was made for
     finally:
         plan.close()
+
+
+def test_few_rows_long_k():
+    """A plan whose calls have few rows and a long K: its GEMM takes the split-K form with the plan's own
+    workspace, and the result is still the device operators' result bit for bit."""
+    M, K, N, R, dtype = 200, 6144, 512, 32, torch.float16
+    plan, device_path, g = _setup(M, K, N, R, dtype, 11)
+    try:
+        for rows in (200, 200, 64):
+            x = torch.randn(rows, K, generator=g).to(dtype).pin_memory()
+            y = torch.empty(rows, N, dtype=dtype).pin_memory()
+            plan.forward_host(x, y)
+            assert torch.equal(y, device_path(x)), rows
+    finally:
+        plan.close()
+    assert_device_clean()
