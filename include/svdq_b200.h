@@ -168,6 +168,30 @@ int svdq_gemm_w4a4_ws(const void* act, const void* wgt, const void* ascales_swz,
                       unsigned long long workspace_bytes, void* stream);
 
 /*
+ * svdq_gemm_w4a4_ws on a workspace that is part of the library image: no counterpart in the reference.
+ * For callers that must not allocate device memory around the call: a serving loop that has handed
+ * the whole device to its own pool and runs with allocation closed once it is warm; a binding
+ * from another language (cgo, JNI) that has no owner for a device buffer that must outlive the
+ * call; a latency-bound loop that cannot afford the device-wide synchronisation an allocation or
+ * a release may bring.  The function itself allocates and frees nothing, on the host or the device.
+ * The workspace is a static array in device memory of 1024 + 148 * 65536 bytes (9.25 MiB, taken on
+ * every device that loads the library); a call whose split plan (or forced split count, variant
+ * 10000 * S + 128) needs more returns SVDQ_ERR_UNSUPPORTED and launches nothing.  Otherwise the
+ * result is that of svdq_gemm_w4a4_ws with a large enough workspace, bit for bit.
+ * The first call on each device looks the array's address up through the runtime, which may load
+ * the module: make that call before any stream capture is begun on that device.
+ * One array per device and process, shared by every caller: calls on the same device must not
+ * overlap in time (one stream, or ordered by events); two overlapping calls would mix their partial
+ * tiles and tickets.  The ticket counters are zero when the library is loaded and every completed
+ * call leaves them zero, so nothing needs zeroing between calls; after a call whose bounded wait
+ * expired (svdq_device_status != 0) they may be left non-zero and there is no way to clear them
+ * from outside: use the caller-owned workspace form from then on.
+ */
+int svdq_gemm_w4a4_static_ws(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                             const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
+                             const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant, void* stream);
+
+/*
  * Column-sharded (tensor-parallel) form of svdq_gemm_w4a4, one call per GPU: this GPU holds rows
  * [col0, col0 + N) of wgt / wscales / lora_up / wcscales / bias and computes those columns of the
  * [M, N_total] result.  Every finished 32 x 64 strip is written into y_full (this GPU's copy of the

@@ -33,6 +33,7 @@ SIGNATURES = {
     "svdq_gemm_w4a4": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p]),
     "svdq_gemm_w4a4_workspace_bytes": (c_ulonglong, [c_int, c_int, c_int, c_int]),
     "svdq_gemm_w4a4_ws": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p, c_ulonglong, c_void_p]),
+    "svdq_gemm_w4a4_static_ws": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p]),
     "svdq_gemm_w4a4_columns": (c_int, [c_void_p] * 10 + [POINTER(c_void_p)] + [c_int] * 9 + [c_void_p]),
     "svdq_gemm_w4a4_supported": (c_int, [c_int, c_int, c_int, c_int]),
     "svdq_device_status": (c_int, [POINTER(c_uint)]),

@@ -212,6 +212,40 @@ int svdq_device_status(unsigned int out[4]) {
 }
 
 // ---------------------------------------------------------------------------
+// split-K GEMM on a workspace that is part of the library image
+// ---------------------------------------------------------------------------
+// Room for the ticket counters and 148 partial tiles of 128 x 128 fp32 (tiles x splits never exceeds the
+// SM count, 148 on this part): 9.25 MiB of device memory per device that loads the library, there
+// whether or not the entry point below is ever called.  Static storage: zero when the module is loaded.
+constexpr size_t kStaticWsPartials = 148;
+constexpr size_t kStaticWsBytes = kSplitTicketBytes + kStaticWsPartials * (128 * 128 * 4);
+static __device__ __align__(256) unsigned char g_static_ws[kStaticWsBytes];
+
+int svdq_gemm_w4a4_static_ws(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                             const void* lora_act16, const void* lora_up, const void* lora_up_f16,
+                             const void* wcscales, const void* bias, void* y, int M, int N, int K, int R, int dtype,
+                             int variant, void* stream) {
+  if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
+  // what this call would park in the workspace: the library's own plan, or the forced split count
+  size_t need = 0;
+  if (variant == 0) need = gemm_split_workspace_bytes(M, N, K, R);
+  else if (variant >= 10000)
+    need = kSplitTicketBytes + static_cast<size_t>(M / 128) * (N / 128) * (variant / 10000) * (128 * 128 * 4);
+  if (need > kStaticWsBytes) return SVDQ_ERR_UNSUPPORTED;
+  // the array's address on the current device, looked up once per device and kept
+  static void* addr[64] = {};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SVDQ_ERR_CUDA;
+  if (addr[dev] == nullptr) {
+    void* a = nullptr;
+    if (cudaGetSymbolAddress(&a, g_static_ws) != cudaSuccess || a == nullptr) { cudaGetLastError(); return SVDQ_ERR_CUDA; }
+    addr[dev] = a;
+  }
+  return gemm_entry(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R,
+                    dtype, variant, addr[dev], kStaticWsBytes, stream);
+}
+
+// ---------------------------------------------------------------------------
 // host-buffer plan
 // ---------------------------------------------------------------------------
 // Two slots of per-call buffers and three streams (host->device, compute, device->host), so that the
