@@ -321,12 +321,13 @@ _SPLIT_WS: dict = {}
 
 
 def _split_workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
-    """Split-K workspace of the current stream of `dev` (zeroed when made; every call leaves its ticket
-    counters zero).  One per stream, because calls that share a workspace must not overlap."""
+    """Split-K workspace of the current stream of `dev` (ticket counters zeroed when made; every call
+    leaves them zero).  One per stream, because calls that share a workspace must not overlap."""
     key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev))
     ws = _SPLIT_WS.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.zeros(max(nbytes, 10 << 20), dtype=torch.uint8, device=dev)
+        ws = torch.empty(max(nbytes, 10 << 20), dtype=torch.uint8, device=dev)
+        ws[:1024].zero_()                      # the ticket counters; the partial tiles need no initial value
         _SPLIT_WS[key] = ws
     return ws
 
