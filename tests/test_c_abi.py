@@ -71,6 +71,17 @@ def test_argument_validation_needs_no_device(lib_path):
     assert dst.tolist() == [1.0, -0.0078125, 0.0, 2.0]
     big = np.array([0x4800], dtype=np.uint16)                                   # 131072 as bf16
     assert lib.svdq_lora_up_to_f16(big.ctypes.data, dst.ctypes.data, 1) == 7
+    # split-K workspace: only for few tiles and a long K; ticket block + tiles x splits partial tiles of 64 KB
+    assert lib.svdq_gemm_w4a4_workspace_bytes(256, 3072, 10240, 32) == 1024 + 48 * 3 * 65536
+    assert lib.svdq_gemm_w4a4_workspace_bytes(256, 3840, 15360, 128) == 1024 + 60 * 2 * 65536
+    assert lib.svdq_gemm_w4a4_workspace_bytes(256, 3072, 3840, 128) == 0          # K too short to repay the split
+    assert lib.svdq_gemm_w4a4_workspace_bytes(4352, 3072, 10240, 32) == 0         # plenty of tiles
+    assert lib.svdq_gemm_w4a4_workspace_bytes(100, 3072, 10240, 32) == 0          # not a supported shape
+    # the workspace forms check their arguments like the plain call, before anything is launched
+    assert lib.svdq_gemm_w4a4_ws(p, p, p, p, None, None, None, None, None, p, 100, 128, 128, 0, 0, 0, p, 4096, None) == 2
+    assert lib.svdq_gemm_w4a4_ws(p, p, p, p, None, None, None, None, None, p, 128, 128, 128, 0, 0, 0, p + 4, 4096, None) == 4
+    assert lib.svdq_gemm_w4a4_static_ws(p, p, p, p, None, None, None, None, None, p, 100, 128, 128, 0, 0, 0, None) == 2
+    assert lib.svdq_gemm_w4a4_static_ws(p, p, p, p, None, None, None, None, None, p, 256, 3072, 10240, 0, 0, 40128, None) == 7
 
 
 def test_operator_asserts_mirror_the_reference(lib_path):
