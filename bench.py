@@ -145,8 +145,8 @@ def run_reference(args):
     except Exception:
         pass
     from oracle import nvfp4_oracle as O
-    from svdquant_kernels_b200.workloads import CONFIGS, make_inputs
-    shape = CONFIGS[args.config]
+    from svdquant_kernels_b200.workloads import CONFIGS, SMALL_M, make_inputs
+    shape = CONFIGS.get(args.config) or SMALL_M[args.config]
     rows = min(shape.M, args.cpu_rows)
     inp = make_inputs(shape, m_rows=rows)
     name = "fp16" if shape.dtype == torch.float16 else "bf16"
@@ -189,7 +189,7 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     from svdquant_kernels_b200 import _lib, ops
-    from svdquant_kernels_b200.workloads import CONFIGS, gemm_flops, make_inputs, quantizer_bytes
+    from svdquant_kernels_b200.workloads import CONFIGS, SMALL_M, gemm_flops, make_inputs, quantizer_bytes
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -202,7 +202,7 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
 
-    shape = CONFIGS[args.config]
+    shape = CONFIGS.get(args.config) or SMALL_M[args.config]
     name = "fp16" if shape.dtype == torch.float16 else "bf16"
     # every rank: its own rows, the same weights
     inp = make_inputs(shape, row_offset=rank)
@@ -429,7 +429,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--config", default="c1")
+    ap.add_argument("--config", default="c1", help="c1..c4 (benchmark configurations) or s0..s2 (a few hundred rows)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-rows", type=int, default=1024, help="rows per pass of the CPU oracle sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -41,6 +41,13 @@ CONFIGS: dict[str, LinearShape] = {
     "c3": LinearShape("c3", 4352, 15360, 3840, 128, torch.bfloat16, act="gelu"),
     "c4": LinearShape("c4", 4352, 10240, 3072, 32, torch.float16),
 }
+# A few hundred rows (the small-M shapes of the reference's GEMM_SHAPES, cute_kernels/gemm_w4a4/harness.py:17-24,
+# and their long-K relatives): not benchmark configurations, but `bench.py --config s0..s2` times them too.
+SMALL_M: dict[str, LinearShape] = {
+    "s0": LinearShape("s0", 256, 3840, 3072, 128, torch.float16),
+    "s1": LinearShape("s1", 256, 10240, 3072, 32, torch.float16),
+    "s2": LinearShape("s2", 256, 15360, 3840, 128, torch.bfloat16, act="gelu"),
+}
 _SEED_BASE = 1234
 
 
