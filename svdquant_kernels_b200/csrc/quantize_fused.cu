@@ -7,7 +7,7 @@
 // (triton_kernels/quantize_w4a4_act_fuse_lora/kernel.py:115-286); results
 // follow baseline/kernels/quantize_w4a4_act_fuse_lora/ref.py:19-50.
 //
-// Decomposition.  A cluster of KS (1 or 2) CTAs owns one tile of 64 rows; CTA k
+// Decomposition.  A cluster of KS (1, 2, 4 or 8) CTAs owns one tile of 64 rows; CTA k
 // owns a contiguous range of 64-column slabs of K.  Per slab the producer warp
 // TMA-loads the x tile (64 x 64, 128-byte swizzle) and the matching lora_down
 // slab (64 x R) into one ring stage, together with the slab's 64 entries of
@@ -15,9 +15,11 @@
 // Two consumers read the stage: the MMA warp accumulates x_tile @ lora_down_slab
 // into a [64 x R] fp32 accumulator in tensor memory, and sixteen quantize warps
 // turn the tile into codes and scales.  x is read from HBM exactly once.  With
-// KS = 2 the two partial accumulators are summed in a fixed order through
+// KS > 1 the partial accumulators are summed in a fixed order through
 // distributed shared memory: no atomics, no zero-fill, no scratch in global
-// memory.  (64-row tiles with pairs, not 128-row tiles with quads: a B200 keeps
+// memory.  Large inputs run with KS = 2; clusters of 4 and 8 are for inputs of
+// a few hundred rows, where pairs would leave most SMs idle (256 x 10240:
+// 36.0 -> 12.9 us), and are taken only if all of them are resident at once.  (64-row tiles with pairs, not 128-row tiles with quads: a B200 keeps
 // at most 33 four-CTA clusters of this size resident, one short of the 34 row
 // tiles of a 4352-row activation, while 68 pairs fit in one wave.  128-row tiles
 // whose K ranks meet through global memory were measured too: what they save in
@@ -473,7 +475,10 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     uint32_t* flags = lora16_flags(p.lora16, static_cast<size_t>(p.M_pad) * p.R);
     const uint32_t unfit = *lora_unfit;
     if (ks == 1) { flags[m0 / 32] = unfit; flags[m0 / 32 + 1] = unfit; }
-    else flags[m0 / 32 + krank] = unfit;
+    else if (ks == 2) flags[m0 / 32 + krank] = unfit;
+    // KS > 2: several CTAs wrote rows of the same 32-row block and none knows the others' verdict, so
+    // all of them store the same "no promise" value (the GEMM then takes its two-pass bf16 route)
+    else flags[m0 / 32 + krank / (ks / 2)] = 1u;
   }
   if (*abort_flag) {
     const unsigned long long t0 = globaltimer_ns();
@@ -509,27 +514,34 @@ __global__ void smooth_table_kernel(const T* __restrict__ smooth, float2* __rest
 }  // namespace qf
 
 // How many CTAs share one row tile along K (0 = no admissible split).
-static int pick_k_split(int M_pad, int K) {
+// Clusters of 4 and 8 serve inputs of a few hundred to a couple of thousand rows, where two CTAs per
+// row tile would leave most SMs idle; they are taken only if all of them can be resident at once
+// (max4 / max8: clusters of that size the device can hold).  Cost in slabs; the constant is the
+// cluster reduction of the LoRA partial sums.
+static int pick_k_split(int M_pad, int K, int max4, int max8) {
   const int tiles = M_pad / qf::TILE_M;
   const int slabs = K / qf::SLAB_K;
   const int sms = sm_count();
   int best = 0;
   double best_cost = 1e30;
-  for (int ks : {1, 2}) {
+  for (int ks : {1, 2, 4, 8}) {
     if (ks > slabs) continue;
     const int ctas = tiles * ks;
+    if (ks > 2 && (ctas > sms || tiles > (ks == 4 ? max4 : max8))) continue;
     const int waves = (ctas + sms - 1) / sms;
-    const double cost = static_cast<double>(waves) * ((slabs + ks - 1) / ks) + 2.0 * (ks > 1);
+    const double cost = static_cast<double>(waves) * ((slabs + ks - 1) / ks) + (ks == 1 ? 0.0 : ks == 2 ? 2.0 : 1.0 + 0.5 * ks);
     if (cost < best_cost) { best_cost = cost; best = ks; }
   }
   return best;
 }
 
+template <typename T, int RP> static int max_clusters_t(int ks);
+
 bool quantize_fused_supported(int M, int K, int R, int M_pad) {
   if (M <= 0 || K <= 0 || M_pad < M) return false;
   if (M_pad % qf::TILE_M != 0 || K % qf::SLAB_K != 0) return false;
   if (R < 0 || R > 256 || R % 8 != 0) return false;
-  return pick_k_split(M_pad, K) != 0;
+  return pick_k_split(M_pad, K, 0, 0) != 0;
 }
 
 int launch_smooth_table(const void* smooth, void* table, int K, int dtype, cudaStream_t stream) {
@@ -562,7 +574,15 @@ static int launch_qf(const void* x, const void* w, const qf::Params& p, cudaStre
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess) return SVDQ_ERR_LAUNCH;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  int ks = pick_k_split(p.M_pad, p.K);
+  static int cap4[64], cap8[64];
+  static bool capped[64] = {};
+  if (dev >= 0 && dev < 64 && !capped[dev]) {
+    cap4[dev] = max_clusters_t<T, RP>(4);
+    cap8[dev] = max_clusters_t<T, RP>(8);
+    capped[dev] = true;
+  }
+  const bool known = dev >= 0 && dev < 64;
+  int ks = pick_k_split(p.M_pad, p.K, known ? cap4[dev] : 0, known ? cap8[dev] : 0);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.M_pad / qf::TILE_M, ks, 1);
   cfg.blockDim = dim3(qf::NUM_THREADS, 1, 1);

@@ -57,7 +57,11 @@ def _check(x, ld, sm, force, pad=256):
             blocks = -(-la.shape[0] // 32)
             unfit = np.array([not (np.abs(la[32 * b:32 * b + 32]) <= 65504.0).all() for b in range(blocks)])
             if force == FUSED:
-                assert ((flags[:blocks] != 0) == unfit).all(), "fits-fp16 words of lora_act differ"
+                # a zero word promises that the 32 rows fit fp16; with few row tiles (more than two CTAs
+                # per tile) the kernel makes no promise, otherwise the words are exact
+                assert not ((flags[:blocks] == 0) & unfit).any(), "a row block that does not fit fp16 is marked as fitting"
+                if (la.shape[0] // 64) * 4 > 148:
+                    assert ((flags[:blocks] != 0) == unfit).all(), "fits-fp16 words of lora_act differ"
             else:
                 assert (flags[:blocks] != 0).all(), "the CUDA-core path must mark every row block"
     return act, ascales, lora
