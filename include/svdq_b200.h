@@ -184,8 +184,9 @@ int svdq_gemm_w4a4_ws(const void* act, const void* wgt, const void* ascales_swz,
  * overlap in time (one stream, or ordered by events); two overlapping calls would mix their partial
  * tiles and tickets.  The ticket counters are zero when the library is loaded and every completed
  * call leaves them zero, so nothing needs zeroing between calls; after a call whose bounded wait
- * expired (svdq_device_status != 0) they may be left non-zero and there is no way to clear them
- * from outside: use the caller-owned workspace form from then on.
+ * expired they may be left non-zero: svdq_device_status, when it reports such a failure, also puts
+ * the counters of the current device's array back to zero (a memset, nothing is allocated), so
+ * read the status on that device before the next call of this entry point.
  */
 int svdq_gemm_w4a4_static_ws(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
                              const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
@@ -215,9 +216,22 @@ int svdq_gemm_w4a4_supported(int M, int N, int K, int R);
 /*
  * Reads (and clears) the device status word that kernels write when a bounded
  * wait expires.  Synchronises the device.  out[0]=code (0 = clean), out[1]=block,
- * out[2]=tag, out[3]=how many waits gave up.
+ * out[2]=tag, out[3]=how many waits gave up.  When it reports a failure it also
+ * zeroes the ticket counters of the library's static split-K workspace on the
+ * current device (see svdq_gemm_w4a4_static_ws).
  */
 int svdq_device_status(unsigned int out[4]);
+
+/*
+ * Self-test of the bounded waits every kernel of this library uses: launches one warp that waits,
+ * with the library's own wait routine, on a barrier nothing arrives on.  After limit_ns (at most
+ * 1e8) the wait gives up, records code 6 with tag 0x5E1F in the status word and the kernel ends
+ * normally; svdq_device_status then returns SVDQ_ERR_DEVICE once and the device stays usable.
+ * seen_device (optional, 4 bytes of device memory) receives bit 0 = first wait succeeded, bit 1 =
+ * second wait succeeded, bit 2 = the CTA's abort flag was raised; expected value 4.
+ * No counterpart in the reference (its kernels have unbounded waits).
+ */
+int svdq_selftest_wait_expiry(unsigned long long limit_ns, unsigned int* seen_device, void* stream);
 
 /*
  * Whole linear from HOST buffers: copies x to the device, runs quantizer and

@@ -2,6 +2,7 @@
 // argument validation, dispatch between the fused and the generic quantizer,
 // the device status word, and the host-buffer "plan" used for end-to-end runs.
 #include <cstring>
+#include <mutex>
 #include <new>
 
 #include <cuda_bf16.h>
@@ -130,7 +131,7 @@ int svdq_lora_up_to_f16(const void* lora_up_bf16_host, void* out_f16_host, long 
 }
 
 int svdq_quantizer_max_active_clusters(int R, int k_split, int dtype) {
-  if (k_split != 1 && k_split != 2 && k_split != 4) return -1;
+  if (k_split != 1 && k_split != 2 && k_split != 4 && k_split != 8) return -1;
   return quantize_fused_max_clusters(R, k_split, dtype);
 }
 
@@ -203,14 +204,6 @@ int svdq_gemm_w4a4_columns(const void* act, const void* wgt, const void* ascales
                           M, N, K, R, dtype, variant, tp, static_cast<cudaStream_t>(stream));
 }
 
-int svdq_device_status(unsigned int out[4]) {
-  unsigned int tmp[4] = {0, 0, 0, 0};
-  int rc = read_and_clear_status(tmp);
-  if (out != nullptr)
-    for (int i = 0; i < 4; ++i) out[i] = tmp[i];
-  return rc;
-}
-
 // ---------------------------------------------------------------------------
 // split-K GEMM on a workspace that is part of the library image
 // ---------------------------------------------------------------------------
@@ -220,6 +213,42 @@ int svdq_device_status(unsigned int out[4]) {
 constexpr size_t kStaticWsPartials = 148;
 constexpr size_t kStaticWsBytes = kSplitTicketBytes + kStaticWsPartials * (128 * 128 * 4);
 static __device__ __align__(256) unsigned char g_static_ws[kStaticWsBytes];
+
+// The array's address on each device, looked up once (cudaGetSymbolAddress) under a mutex: first calls
+// may come from several host threads at once.
+static std::mutex g_static_ws_mutex;
+static void* g_static_ws_addr[64] = {};
+
+static int static_ws_address(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SVDQ_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_static_ws_mutex);
+  if (g_static_ws_addr[dev] == nullptr) {
+    void* a = nullptr;
+    if (cudaGetSymbolAddress(&a, g_static_ws) != cudaSuccess || a == nullptr) { cudaGetLastError(); return SVDQ_ERR_CUDA; }
+    g_static_ws_addr[dev] = a;
+  }
+  *out = g_static_ws_addr[dev];
+  return SVDQ_OK;
+}
+
+// A kernel that gave up on a bounded wait may have left ticket counters of the static workspace
+// non-zero; every later split call on it would then draw tickets that never reach "last" and write
+// no output.  Reading a failure therefore also puts the counters of the current device's array back
+// to zero (the device is idle here: the read synchronised it).  Nothing is allocated.
+int svdq_device_status(unsigned int out[4]) {
+  unsigned int tmp[4] = {0, 0, 0, 0};
+  int rc = read_and_clear_status(tmp);
+  if (rc == SVDQ_ERR_DEVICE) {
+    void* ws = nullptr;
+    if (static_ws_address(&ws) != SVDQ_OK || cudaMemset(ws, 0, kSplitTicketBytes) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess)
+      rc = SVDQ_ERR_CUDA;
+  }
+  if (out != nullptr)
+    for (int i = 0; i < 4; ++i) out[i] = tmp[i];
+  return rc;
+}
 
 int svdq_gemm_w4a4_static_ws(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
                              const void* lora_act16, const void* lora_up, const void* lora_up_f16,
@@ -233,16 +262,45 @@ int svdq_gemm_w4a4_static_ws(const void* act, const void* wgt, const void* ascal
     need = kSplitTicketBytes + static_cast<size_t>(M / 128) * (N / 128) * (variant / 10000) * (128 * 128 * 4);
   if (need > kStaticWsBytes) return SVDQ_ERR_UNSUPPORTED;
   // the array's address on the current device, looked up once per device and kept
-  static void* addr[64] = {};
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SVDQ_ERR_CUDA;
-  if (addr[dev] == nullptr) {
-    void* a = nullptr;
-    if (cudaGetSymbolAddress(&a, g_static_ws) != cudaSuccess || a == nullptr) { cudaGetLastError(); return SVDQ_ERR_CUDA; }
-    addr[dev] = a;
-  }
+  void* ws = nullptr;
+  const int rc = static_ws_address(&ws);
+  if (rc != SVDQ_OK) return rc;
   return gemm_entry(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R,
-                    dtype, variant, addr[dev], kStaticWsBytes, stream);
+                    dtype, variant, ws, kStaticWsBytes, stream);
+}
+
+// ---------------------------------------------------------------------------
+// self-test of the bounded wait
+// ---------------------------------------------------------------------------
+}  // extern "C"
+
+namespace svdq {
+// One warp waits on a barrier of its own that nothing ever arrives on, with the same mbar_wait the
+// kernels use but a caller-given limit; when the limit runs out the wait records its code in the
+// status word and returns false, the kernel notes what it saw and ends normally.
+__global__ void wait_expiry_selftest_kernel(unsigned long long limit_ns, unsigned int* seen) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const WaitCtx ctx{&abort_flag};
+  const bool ok = mbar_wait(&bar, 0, ctx, kDevWaitMisc, 0x5E1Fu, limit_ns);
+  // a second wait in an aborted CTA returns at once
+  const bool again = mbar_wait(&bar, 0, ctx, kDevWaitMisc, 0x5E20u, limit_ns);
+  if (threadIdx.x == 0 && seen != nullptr) *seen = (ok ? 1u : 0u) | (again ? 2u : 0u) | (abort_flag ? 4u : 0u);
+}
+}  // namespace svdq
+
+extern "C" {
+
+int svdq_selftest_wait_expiry(unsigned long long limit_ns, unsigned int* seen_device, void* stream) {
+  if (limit_ns == 0 || limit_ns > 100000000ull) return SVDQ_ERR_SHAPE;      // at most 0.1 s
+  wait_expiry_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns, seen_device);
+  return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;
 }
 
 // ---------------------------------------------------------------------------

@@ -131,7 +131,8 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
 // Bounded wait.  Returns false (after recording `code`) if the phase never
 // completed or the CTA had already aborted.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx,
-                                          unsigned int code, unsigned int tag) {
+                                          unsigned int code, unsigned int tag,
+                                          unsigned long long limit_ns = SVDQ_WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   unsigned long long t0 = 0;
   uint32_t spins = 0;
@@ -141,7 +142,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     if ((++spins & 0x3F) == 0) {
       unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > SVDQ_WAIT_LIMIT_NS) {
+      else if (now - t0 > limit_ns) {
         report_failure(ctx, code, tag);
         return false;
       }

@@ -23,8 +23,61 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// Encoded descriptors are kept in a small direct-mapped table keyed by everything that goes into one
+// (a descriptor holds an address and extents, never data, so an entry cannot go stale): a serving
+// loop that calls with the same buffers again encodes nothing.  Guarded by a mutex; a collision
+// just re-encodes.
+namespace {
+struct TmapKey {
+  const void* base;
+  uint64_t rows, cols, stride;
+  uint32_t box_rows, box_cols;
+  int elem_bytes, swz;
+  bool operator==(const TmapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && stride == o.stride && box_rows == o.box_rows &&
+           box_cols == o.box_cols && elem_bytes == o.elem_bytes && swz == o.swz;
+  }
+};
+struct TmapEntry {
+  TmapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+constexpr int kTmapCacheSlots = 512;
+TmapEntry g_tmap_cache[kTmapCacheSlots];
+std::mutex g_tmap_mutex;
+
+inline uint32_t tmap_slot(const TmapKey& k) {
+  uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+  h ^= (k.rows * 0xC2B2AE3D27D4EB4Full) ^ (k.cols << 17) ^ (k.stride << 3) ^ (static_cast<uint64_t>(k.box_rows) << 40) ^
+       (static_cast<uint64_t>(k.box_cols) << 52) ^ static_cast<uint64_t>(k.elem_bytes * 4 + k.swz);
+  h ^= h >> 29;
+  return static_cast<uint32_t>(h % kTmapCacheSlots);
+}
+}  // namespace
+
+static int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                          uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols, TmapSwizzle swz);
+
 int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
                  uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols, TmapSwizzle swz) {
+  const TmapKey key{base, rows, cols, row_stride_bytes, box_rows, box_cols, elem_bytes, static_cast<int>(swz)};
+  const uint32_t slot = tmap_slot(key);
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mutex);
+    const TmapEntry& e = g_tmap_cache[slot];
+    if (e.valid && e.key == key) { *out = e.map; return SVDQ_OK; }
+  }
+  const int rc = encode_tmap_2d(out, base, elem_bytes, rows, cols, row_stride_bytes, box_rows, box_cols, swz);
+  if (rc != SVDQ_OK) return rc;
+  std::lock_guard<std::mutex> lock(g_tmap_mutex);
+  TmapEntry& e = g_tmap_cache[slot];
+  e.key = key; e.map = *out; e.valid = true;
+  return SVDQ_OK;
+}
+
+static int encode_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t rows, uint64_t cols,
+                          uint64_t row_stride_bytes, uint32_t box_rows, uint32_t box_cols, TmapSwizzle swz) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return SVDQ_ERR_LAUNCH;
   CUtensorMapDataType dt;

@@ -35,7 +35,7 @@ import torch
 from . import _lib
 
 _DT = {torch.float16: _lib.DTYPE_F16, torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_F32}
-_TWIN = "_svdq_twin"   # attribute name: (tensor, version of the owner when it was made)
+_TWIN = "_svdq_twins"  # attribute of the owner's storage object: {(offset, numel): (twin, owner version)}
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -47,17 +47,49 @@ def _stream(device: torch.device) -> int:
 
 
 def _attach(owner: torch.Tensor, twin: torch.Tensor) -> None:
-    setattr(owner, _TWIN, (twin, owner._version, owner.data_ptr()))
+    """Remember `twin` as the derived form of `owner`'s current contents.
+
+    The record hangs on the owner's storage object, not on the tensor wrapper: a tensor that went
+    through the dispatcher (torch.ops.*), a view or a detach() is a new wrapper around the same
+    storage, and the storage object lives exactly as long as the memory does, so a record can
+    neither be lost on the way nor outlive its data and be found by a later tensor at the same
+    address.  The owner's version counter (bumped by every in-place torch op) guards against
+    edits after the fact."""
+    st = owner.untyped_storage()
+    recs = getattr(st, _TWIN, None)
+    if recs is None:
+        recs = {}
+        setattr(st, _TWIN, recs)
+    recs[(owner.storage_offset(), owner.numel())] = (twin, owner._version)
 
 
-def _attached(owner: torch.Tensor) -> Optional[torch.Tensor]:
-    rec = getattr(owner, _TWIN, None)
-    if rec is None:
+def _attached(owner: torch.Tensor, any_version: bool = False) -> Optional[torch.Tensor]:
+    recs = getattr(owner.untyped_storage(), _TWIN, None)
+    if recs is None:
         return None
-    twin, version, ptr = rec
-    if owner._version != version or owner.data_ptr() != ptr:
+    rec = recs.get((owner.storage_offset(), owner.numel()))
+    if rec is None or (rec[1] != owner._version and not any_version):
         return None
-    return twin
+    return rec[0]
+
+
+class _on_device:
+    """`with torch.cuda.device(dev)` only when `dev` is not already current (the switch costs
+    several microseconds of host time per call, more than the launch itself)."""
+    __slots__ = ("ctx",)
+
+    def __init__(self, dev: torch.device):
+        idx = dev.index
+        self.ctx = None if idx is None or idx == torch.cuda.current_device() else torch.cuda.device(idx)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            self.ctx.__exit__(*exc)
+        return False
 
 
 def _smooth_table(smooth: torch.Tensor) -> torch.Tensor:
@@ -68,7 +100,7 @@ def _smooth_table(smooth: torch.Tensor) -> torch.Tensor:
     K = smooth.shape[0]
     lib = _lib.load()
     table = torch.empty(2 * K + 4, dtype=torch.float32, device=smooth.device)
-    with torch.cuda.device(smooth.device):
+    with _on_device(smooth.device):
         rc = lib.svdq_prepare_smooth(_ptr(smooth), _ptr(table), K, _DT[smooth.dtype], _stream(smooth.device))
     _lib.check(rc, "prepare_smooth")
     _attach(smooth, table)
@@ -85,8 +117,11 @@ def quantize_w4a4_act_fuse_lora(
     block_m: int = 64,          # accepted for call-site compatibility; the kernel picks its own tiling
     block_n: int = 64,
     k_splits: Optional[int] = None,
+    out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
     _force: int = _lib.QUANT_AUTO,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """`out = (act, ascales, lora_act)` writes into tensors of a previous call (same shapes) instead
+    of allocating; their layout twins are reused as well, so a steady-state call allocates nothing."""
     assert input.dim() == 2 and lora_down.dim() == 2
     assert input.is_cuda and lora_down.is_cuda
     assert input.dtype == lora_down.dtype
@@ -111,17 +146,28 @@ def quantize_w4a4_act_fuse_lora(
     table = None
     if sm is not None and _force != _lib.QUANT_FORCE_GENERIC:
         table = _smooth_table(sm)
-    act = torch.empty((M_pad, K // 2), dtype=torch.uint8, device=dev)
-    ascales = torch.empty((K // 16, M_pad), dtype=torch.float8_e4m3fn, device=dev)
-    lora_act = torch.empty((M_pad, R), dtype=torch.float32, device=dev)
     want_swz = M_pad % 128 == 0 and K % 64 == 0 and M_pad > 0
-    swz = torch.empty(M_pad * (K // 16), dtype=torch.uint8, device=dev) if want_swz else None
+    swz = la16 = None
+    if out is not None:
+        act, ascales, lora_act = out
+        assert act.shape == (M_pad, K // 2) and act.dtype == torch.uint8 and act.is_contiguous() and act.device == dev
+        assert ascales.shape == (K // 16, M_pad) and ascales.dtype == torch.float8_e4m3fn and ascales.is_contiguous()
+        assert lora_act.shape == (M_pad, R) and lora_act.dtype == torch.float32 and lora_act.is_contiguous()
+        swz = _attached(ascales, any_version=True)
+        la16 = _attached(lora_act, any_version=True)
+        if la16 is not None and la16.dtype != input.dtype:
+            la16 = None
+    else:
+        act = torch.empty((M_pad, K // 2), dtype=torch.uint8, device=dev)
+        ascales = torch.empty((K // 16, M_pad), dtype=torch.float8_e4m3fn, device=dev)
+        lora_act = torch.empty((M_pad, R), dtype=torch.float32, device=dev)
+    if want_swz and swz is None:
+        swz = torch.empty(M_pad * (K // 16), dtype=torch.uint8, device=dev)
     # 16-bit form of lora_act for the GEMM: one fp16 plane; or bf16 hi and lo planes, an fp16 plane
     # and the per-32-row "fits fp16" words (a flat buffer, see include/svdq_b200.h)
-    la16 = None
-    if R > 0:
-        la16 = torch.empty(int(lib.svdq_lora_act16_elems(M_pad, R, _DT[input.dtype])), dtype=input.dtype, device=dev)
-    with torch.cuda.device(dev):
+    if R > 0 and la16 is None:
+        la16 = torch.empty(_la16_elems(M_pad, R, input.dtype), dtype=input.dtype, device=dev)
+    with _on_device(dev):
         rc = lib.svdq_quantize_w4a4_act_fuse_lora(
             _ptr(x), _ptr(ld), _ptr(sm), _ptr(table), _ptr(act), _ptr(ascales), _ptr(lora_act), _ptr(swz), _ptr(la16),
             M, K, R, M_pad, _DT[input.dtype], _force, _stream(dev))
@@ -131,6 +177,17 @@ def quantize_w4a4_act_fuse_lora(
     if la16 is not None:
         _attach(lora_act, la16)
     return act, ascales, lora_act
+
+
+_LA16_ELEMS: dict = {}
+
+
+def _la16_elems(rows: int, R: int, dtype: torch.dtype) -> int:
+    key = (rows, R, dtype)
+    n = _LA16_ELEMS.get(key)
+    if n is None:
+        n = _LA16_ELEMS[key] = int(_lib.load().svdq_lora_act16_elems(rows, R, _DT[dtype]))
+    return n
 
 
 def quantize_nvfp4_rows(x: torch.Tensor, *, pad_size: int = 1) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -147,7 +204,7 @@ def quantize_nvfp4_rows(x: torch.Tensor, *, pad_size: int = 1) -> Tuple[torch.Te
     scales = torch.empty((K // 16, rows_pad), dtype=torch.float8_e4m3fn, device=dev)
     want_swz = rows_pad % 128 == 0 and K % 64 == 0 and rows_pad > 0
     swz = torch.empty(rows_pad * (K // 16), dtype=torch.uint8, device=dev) if want_swz else None
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = lib.svdq_quantize_nvfp4_rows(_ptr(xc), _ptr(packed), _ptr(scales), _ptr(swz), rows, rows_pad, K,
                                           _DT[x.dtype], _stream(dev))
     _lib.check(rc, "quantize_nvfp4_rows")
@@ -167,7 +224,7 @@ def swizzle_scales(scales: torch.Tensor) -> torch.Tensor:
     lib = _lib.load()
     src = scales.contiguous()
     out = torch.empty(G * rows, dtype=torch.uint8, device=scales.device)
-    with torch.cuda.device(scales.device):
+    with _on_device(scales.device):
         rc = lib.svdq_swizzle_scales(_ptr(src), _ptr(out), G, rows, _stream(scales.device))
     _lib.check(rc, "swizzle_scales")
     _attach(scales, out)
@@ -185,8 +242,8 @@ def _lora_act_16(lora_act_in: torch.Tensor, out_dtype: torch.dtype) -> torch.Ten
     lib = _lib.load()
     src = src.contiguous()
     rows, R = src.shape
-    out = torch.empty(int(lib.svdq_lora_act16_elems(rows, R, _DT[out_dtype])), dtype=out_dtype, device=src.device)
-    with torch.cuda.device(src.device):
+    out = torch.empty(_la16_elems(rows, R, out_dtype), dtype=out_dtype, device=src.device)
+    with _on_device(src.device):
         rc = lib.svdq_cast_lora_act(_ptr(src), _ptr(out), rows, R, _DT[out_dtype], _stream(src.device))
     _lib.check(rc, "cast_lora_act")
     return out
@@ -220,6 +277,7 @@ def gemm_w4a4(
     use_2cta: bool = False,                 # accepted for call-site compatibility
     tiler_mn: Optional[Tuple[int, int]] = None,
     lora_schedule: str = "interleave",
+    out: Optional[torch.Tensor] = None,
     _columns: Optional[Tuple[torch.Tensor, list, int]] = None,
     _splits: Optional[int] = None,
 ) -> torch.Tensor:
@@ -291,13 +349,17 @@ def gemm_w4a4(
         n_total = y_full.shape[1]
         assert 0 <= col0 and col0 + N <= n_total and col0 % 64 == 0 and len(peer_ptrs) <= 7
         arr = (ctypes.c_void_p * max(1, len(peer_ptrs)))(*peer_ptrs)
-        with torch.cuda.device(dev):
+        with _on_device(dev):
             rc = lib.svdq_gemm_w4a4_columns(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc),
                                             _ptr(b), _ptr(y_full), arr, len(peer_ptrs), n_total, col0, M, N, K, R,
                                             _DT[out_dtype], variant, _stream(dev))
         _lib.check(rc, "gemm_w4a4_columns")
         return y_full
-    y = torch.empty((M, N), dtype=out_dtype, device=dev)
+    if out is not None:
+        assert out.shape == (M, N) and out.dtype == out_dtype and out.is_contiguous() and out.device == dev
+        y = out
+    else:
+        y = torch.empty((M, N), dtype=out_dtype, device=dev)
     ws = None
     if _splits is not None and _splits > 1:
         variant = 10000 * _splits + 128
@@ -306,7 +368,7 @@ def gemm_w4a4(
         need = int(lib.svdq_gemm_w4a4_workspace_bytes(M, N, K, R))
         if need > 0:
             ws = _split_workspace(dev, need)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         if ws is not None:
             rc = lib.svdq_gemm_w4a4_ws(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc), _ptr(b),
                                        _ptr(y), M, N, K, R, _DT[out_dtype], variant, _ptr(ws), ws.numel(), _stream(dev))

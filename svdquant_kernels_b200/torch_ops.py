@@ -7,9 +7,10 @@ The reference registers nothing on CUDA and keeps its pod-side registration as a
 Python signatures (triton_kernels/quantize_w4a4_act_fuse_lora/kernel.py:289-400,
 cute_kernels/gemm_w4a4/kernel_v2_fa4.py:113-225).
 
-Tensors that come back from the dispatcher are fresh wrappers, so the layout twins `ops` attaches
-to its outputs (tensor-core scale order, 16-bit lora_act) do not survive the round trip: the GEMM
-rebuilds them with two small kernels.  Code that calls `ops.*` directly keeps them.
+The layout twins `ops` makes next to its outputs (tensor-core scale order, 16-bit lora_act) are
+recorded on the outputs' storage objects, which the dispatcher hands through unchanged, so a
+`torch.ops.svdq_b200.gemm_w4a4` call on the quantizer op's outputs finds them and runs the same
+kernels as the plain Python path; both ops can be captured in a CUDA graph.
 """
 from __future__ import annotations
 

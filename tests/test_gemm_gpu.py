@@ -101,18 +101,25 @@ def test_main_product_is_exact_without_lora():
     assert _case(256, 256, 256, 0, torch.float16, seed=4, wc=False, bias=False) <= 1e-6
 
 
-@pytest.mark.parametrize("cfg", ["c1", "c4"])
+@pytest.mark.parametrize("cfg", ["c1", "c4", "r256"])
 def test_full_size_configs(cfg):
+    """Whole benchmark shapes against the oracle GEMM; "r256" is the rank-256 entry of the reference's
+    GEMM_SHAPES (cute_kernels/gemm_w4a4/harness.py:17-24) at its full size."""
     from svdquant_kernels_b200.workloads import CONFIGS
+    if cfg == "r256":
+        assert _case(4352, 10240, 3072, 256, torch.float16, seed=78) <= TOL
+        return
     s = CONFIGS[cfg]
     assert _case(s.M, s.K, s.N, s.R, s.dtype, seed=77) <= TOL
 
 
 @pytest.mark.parametrize("cfg", ["c2", "c3"])
-def test_largest_configs_whole_output(cfg):
+def test_largest_configs_vs_fp32_matmul_of_dequantised_operands(cfg):
     """The two largest shapes (bf16, 60 N-tiles / 60 K-slabs per tile: many trips round the rings).
-    The oracle dequantises on the CPU; the fp32 products are taken by torch on the GPU so that every
-    element of y is checked, in the reference's order: (main + lora) * wcscales + bias, cast once."""
+    Not the oracle GEMM (too slow at this size on the CPU): the oracle dequantises the operands on the
+    CPU and torch takes the fp32 products on the GPU, so that every element of y is checked, in the
+    reference's order: (main + lora) * wcscales + bias, cast once.  The quantizer outputs that feed
+    it are checked bit for bit against the oracle in test_quantize_gpu.py in the same run."""
     from svdquant_kernels_b200.workloads import CONFIGS, make_inputs
     ops = _ops()
     s = CONFIGS[cfg]

@@ -238,3 +238,43 @@ def test_no_rows_and_strided_input(dtype):
     torch.cuda.synchronize()
     assert_device_clean()
     assert torch.equal(a1, a2) and torch.equal(s1.view(torch.uint8), s2.view(torch.uint8)) and torch.equal(l1, l2)
+
+
+def test_out_argument_reuses_buffers_and_twins():
+    """`out=` writes into the tensors of an earlier call; the layout twins move with them, so a second
+    call allocates nothing and the GEMM sees the new contents."""
+    from svdquant_kernels_b200 import ops
+    g = torch.Generator().manual_seed(31)
+    M, K, R, N, dtype = 512, 512, 32, 256, torch.float16
+    ld = (torch.randn(K, R, generator=g) / K ** 0.5).to(dtype).cuda()
+    sm = (torch.rand(K, generator=g) + 0.5).to(dtype).cuda()
+    lu = (torch.randn(N, R, generator=g) * 0.01).to(dtype).cuda()
+    wgt, wsc = ops.quantize_nvfp4_rows((torch.randn(N, K, generator=g) * 0.02).cuda(), pad_size=1)
+    x1 = torch.randn(M, K, generator=g).to(dtype).cuda()
+    x2 = torch.randn(M, K, generator=g).to(dtype).cuda()
+    q = ops.quantize_w4a4_act_fuse_lora(x1, ld, sm)
+    y = ops.gemm_w4a4(q[0], wgt, q[1], wsc, q[2], lu, None, None, dtype)
+    swz_ptr = ops._attached(q[1]).data_ptr()
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_allocated()
+    q_again = ops.quantize_w4a4_act_fuse_lora(x2, ld, sm, out=q)
+    y_again = ops.gemm_w4a4(q[0], wgt, q[1], wsc, q[2], lu, None, None, dtype, out=y)
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == before
+    assert q_again[0] is q[0] and y_again is y and ops._attached(q[1]).data_ptr() == swz_ptr
+    fresh = ops.quantize_w4a4_act_fuse_lora(x2, ld, sm)
+    y_fresh = ops.gemm_w4a4(fresh[0], wgt, fresh[1], wsc, fresh[2], lu, None, None, dtype)
+    torch.cuda.synchronize()
+    assert torch.equal(q[0], fresh[0]) and torch.equal(q[2], fresh[2]) and torch.equal(y, y_fresh)
+    assert_device_clean()
+
+
+def test_cluster_capacity_query():
+    """How many clusters of 1, 2, 4 and 8 CTAs of the fused kernel the device holds at once: the query
+    answers for every split the kernel can be launched with."""
+    from svdquant_kernels_b200 import _lib
+    lib = _lib.load()
+    caps = {ks: lib.svdq_quantizer_max_active_clusters(128, ks, _lib.DTYPE_F16) for ks in (1, 2, 4, 8)}
+    assert all(v > 0 for v in caps.values()), caps
+    assert caps[1] >= caps[2] >= caps[4] >= caps[8]
+    assert lib.svdq_quantizer_max_active_clusters(128, 3, _lib.DTYPE_F16) == -1
