@@ -40,7 +40,11 @@ enum {
 enum {
   SVDQ_QUANT_AUTO = 0,        /* fused tensor-core kernel when the shape allows, else the generic kernels */
   SVDQ_QUANT_FORCE_GENERIC = 1,
-  SVDQ_QUANT_FORCE_FUSED = 2  /* error instead of falling back */
+  SVDQ_QUANT_FORCE_FUSED = 2, /* the cluster form of the fused kernel; error instead of falling back */
+  /* the streaming form of the fused kernel (tall activations); error if it does not apply.  Tile height
+   * and K split may be forced too: SVDQ_QUANT_FORCE_STREAM | (tile_rows << 8) | (k_split << 4), tile_rows
+   * 128 or 256 (0 = planned), k_split 1, 2, 4 or 8 (0 = planned) */
+  SVDQ_QUANT_FORCE_STREAM = 0x100000
 };
 
 const char* svdq_status_string(int status);
@@ -87,7 +91,30 @@ int svdq_quantize_w4a4_act_fuse_lora(const void* x, const void* lora_down, const
                                      int M, int K, int R, int M_pad, int dtype, int flags, void* stream);
 
 /*
- * How many clusters of `k_split` CTAs (1, 2 or 4) of the fused quantizer the current device can
+ * svdq_quantize_w4a4_act_fuse_lora with a caller-owned workspace in device memory, needed by the
+ * streaming form of the fused kernel (flags = SVDQ_QUANT_FORCE_STREAM ...): CTAs own 128 or 256 rows
+ * and a share of K, and the partial LoRA sums of a row tile meet in the workspace (fp32, added in a
+ * fixed order: results do not depend on timing).  svdq_quantize_workspace_bytes returns the size
+ * the planned tile height and K split of this problem need (0: none); a forced split of k ranks needs
+ * 2048 + k * M_pad * 512 bytes.  With other flags the workspace is ignored and the call is
+ * svdq_quantize_w4a4_act_fuse_lora.  Outputs are identical in codes and scales; lora_act differs
+ * from the other forms only by fp32 summation order.  The library does not choose this form by
+ * itself: on the benchmark shapes it measured a few per cent slower than the cluster form.
+ * The first 2048 bytes of the workspace are counters: zero them once before the first call; every
+ * completed call leaves them zero.  Calls that share a workspace must not overlap in time (same
+ * stream, or ordered by events); after a call whose bounded wait expired (svdq_device_status != 0)
+ * zero them again.  No counterpart in the reference (its Triton kernel adds the partial sums with
+ * atomics into a zero-filled lora_act, triton_kernels/quantize_w4a4_act_fuse_lora/kernel.py:204-286).
+ */
+unsigned long long svdq_quantize_workspace_bytes(int M, int K, int R, int M_pad);
+int svdq_quantize_w4a4_act_fuse_lora_ws(const void* x, const void* lora_down, const void* smooth,
+                                        const void* smooth_table, void* act, void* ascales, float* lora_act,
+                                        void* ascales_swz, void* lora_act16, int M, int K, int R, int M_pad,
+                                        int dtype, int flags, void* workspace, unsigned long long workspace_bytes,
+                                        void* stream);
+
+/*
+ * How many clusters of `k_split` CTAs (1, 2, 4 or 8) of the fused quantizer the current device can
  * keep resident at once for LoRA rank R; -1 on error.  Introspection for tuning; the reference
  * has no counterpart (its Triton launch picks k_splits from a table,
  * triton_kernels/quantize_w4a4_act_fuse_lora/kernel.py:344-378).

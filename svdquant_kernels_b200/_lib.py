@@ -14,7 +14,7 @@ _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG_DIR, "libsvdq_b200.so")
 
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
-QUANT_AUTO, QUANT_FORCE_GENERIC, QUANT_FORCE_FUSED = 0, 1, 2
+QUANT_AUTO, QUANT_FORCE_GENERIC, QUANT_FORCE_FUSED, QUANT_FORCE_STREAM = 0, 1, 2, 0x100000
 OK = 0
 
 # name -> (restype, argtypes); kept in the order of include/svdq_b200.h
@@ -24,6 +24,10 @@ SIGNATURES = {
     "svdq_prepare_smooth": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "svdq_quantize_w4a4_act_fuse_lora": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "svdq_quantize_workspace_bytes": (c_ulonglong, [c_int, c_int, c_int, c_int]),
+    "svdq_quantize_w4a4_act_fuse_lora_ws": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                                    c_ulonglong, c_void_p]),
     "svdq_quantizer_max_active_clusters": (c_int, [c_int, c_int, c_int]),
     "svdq_quantize_nvfp4_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "svdq_swizzle_scales": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),

@@ -58,30 +58,59 @@ int svdq_prepare_smooth(const void* smooth, void* smooth_table, int K, int dtype
   return launch_smooth_table(smooth, smooth_table, K, dtype, static_cast<cudaStream_t>(stream));
 }
 
-int svdq_quantize_w4a4_act_fuse_lora(const void* x, const void* lora_down, const void* smooth,
-                                     const void* smooth_table, void* act,
-                                     void* ascales, float* lora_act, void* ascales_swz, void* lora_act16, int M,
-                                     int K, int R, int M_pad, int dtype, int flags, void* stream) {
+static int quantize_entry(const void* x, const void* lora_down, const void* smooth, const void* smooth_table, void* act,
+                          void* ascales, float* lora_act, void* ascales_swz, void* lora_act16, int M, int K, int R,
+                          int M_pad, int dtype, int flags, void* workspace, size_t workspace_bytes, void* stream) {
   if (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16) return SVDQ_ERR_DTYPE;
   if (M < 0 || K <= 0 || R < 0 || M_pad < M || K % 16 != 0) return SVDQ_ERR_SHAPE;
   if (M_pad == 0) return SVDQ_OK;
   if (act == nullptr || ascales == nullptr || (M > 0 && x == nullptr)) return SVDQ_ERR_NULL;
   if (R > 0 && (lora_down == nullptr || lora_act == nullptr)) return SVDQ_ERR_NULL;
   if (!aligned16(x) || !aligned16(act) || !aligned16(smooth) || !aligned16(lora_down) || !aligned16(lora_act) ||
-      !aligned16(ascales_swz) || !aligned16(lora_act16) || !aligned16(smooth_table))
+      !aligned16(ascales_swz) || !aligned16(lora_act16) || !aligned16(smooth_table) || !aligned16(workspace))
     return SVDQ_ERR_ALIGN;
   if (smooth == nullptr && smooth_table != nullptr) return SVDQ_ERR_NULL;
   if (ascales_swz != nullptr && (M_pad % 128 != 0 || K % 64 != 0)) return SVDQ_ERR_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // the fused kernel reads {smooth, 1/smooth} from the prepared table; without one it cannot smooth
-  const bool fused_ok = M > 0 && quantize_fused_supported(M, K, R, M_pad) && (smooth == nullptr || smooth_table != nullptr);
+  // the fused kernels read the smoothing factors from the prepared table; without one they cannot smooth
+  const bool table_ok = smooth == nullptr || smooth_table != nullptr;
+  const bool fused_ok = M > 0 && quantize_fused_supported(M, K, R, M_pad) && table_ok;
   if (flags == SVDQ_QUANT_FORCE_FUSED && !fused_ok) return SVDQ_ERR_UNSUPPORTED;
+  if (flags >= SVDQ_QUANT_FORCE_STREAM) {
+    // The streaming form (128- or 256-row tiles, K ranks met in the workspace) runs only on request: on
+    // every benchmark shape it measured a few per cent behind the cluster form (c1 21.2 vs 18.9 us,
+    // c3 55.6 vs 55.0 us), because both are bound by the quantize warps, not by their data movement.
+    const int tm = (flags >> 8) & 0x1FF, ks = (flags >> 4) & 0xF;
+    if (M <= 0 || !table_ok) return SVDQ_ERR_UNSUPPORTED;
+    return launch_quantize_stream(x, lora_down, smooth_table, act, ascales, lora_act, ascales_swz, lora_act16, M, K, R,
+                                  M_pad, dtype, workspace, workspace != nullptr ? workspace_bytes : 0, tm, ks, st);
+  }
   if (fused_ok && flags != SVDQ_QUANT_FORCE_GENERIC)
     return launch_quantize_fused(x, lora_down, smooth_table, act, ascales, lora_act, ascales_swz, lora_act16, M, K, R,
                                  M_pad, dtype, st);
   int rc = launch_quantize_rows(x, smooth, act, ascales, ascales_swz, M, M_pad, K, dtype, st);
   if (rc != SVDQ_OK) return rc;
   return launch_lora_down(x, lora_down, lora_act, lora_act16, M, M_pad, K, R, dtype, st);
+}
+
+int svdq_quantize_w4a4_act_fuse_lora(const void* x, const void* lora_down, const void* smooth,
+                                     const void* smooth_table, void* act,
+                                     void* ascales, float* lora_act, void* ascales_swz, void* lora_act16, int M,
+                                     int K, int R, int M_pad, int dtype, int flags, void* stream) {
+  return quantize_entry(x, lora_down, smooth, smooth_table, act, ascales, lora_act, ascales_swz, lora_act16, M, K, R, M_pad,
+                        dtype, flags, nullptr, 0, stream);
+}
+
+unsigned long long svdq_quantize_workspace_bytes(int M, int K, int R, int M_pad) {
+  return static_cast<unsigned long long>(quantize_stream_workspace_bytes(M, K, R, M_pad));
+}
+
+int svdq_quantize_w4a4_act_fuse_lora_ws(const void* x, const void* lora_down, const void* smooth,
+                                        const void* smooth_table, void* act, void* ascales, float* lora_act,
+                                        void* ascales_swz, void* lora_act16, int M, int K, int R, int M_pad, int dtype,
+                                        int flags, void* workspace, unsigned long long workspace_bytes, void* stream) {
+  return quantize_entry(x, lora_down, smooth, smooth_table, act, ascales, lora_act, ascales_swz, lora_act16, M, K, R, M_pad,
+                        dtype, flags, workspace, static_cast<size_t>(workspace_bytes), stream);
 }
 
 int svdq_quantize_nvfp4_rows(const void* x, void* codes, void* scales, void* scales_swz, int rows, int rows_pad, int K,
@@ -330,6 +359,8 @@ struct svdq_linear_plan {
   void *wgt, *wscales_swz, *lora_down, *lora_up, *lora_up_f16, *smooth, *smooth_table, *wc, *bias;  // resident weights
   void* split_ws;                                                // split-K workspace of the GEMM (few-row calls, long K), or null
   size_t split_ws_bytes;
+  void* quant_ws;                                                // workspace of the quantizer's streaming form, or null
+  size_t quant_ws_bytes;
 };
 
 static bool is_pinned_host(const void* ptr) {
@@ -406,6 +437,12 @@ int svdq_linear_plan_create(svdq_linear_plan** out, int max_M, int K, int N, int
     if (cudaMalloc(&p->split_ws, p->split_ws_bytes) != cudaSuccess ||
         cudaMemsetAsync(p->split_ws, 0, kSplitTicketBytes, st) != cudaSuccess) rc = SVDQ_ERR_CUDA;
   }
+  if (rc == SVDQ_OK && R > 0) {
+    // calls of any height up to max_M: room for eight K ranks of the tallest one
+    p->quant_ws_bytes = 2048 + static_cast<size_t>(8) * max_M_pad * 128 * 4;
+    if (cudaMalloc(&p->quant_ws, p->quant_ws_bytes) != cudaSuccess ||
+        cudaMemsetAsync(p->quant_ws, 0, 2048, st) != cudaSuccess) rc = SVDQ_ERR_CUDA;
+  }
   if (rc == SVDQ_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = SVDQ_ERR_CUDA;
   if (wscales_dev != nullptr) cudaFree(wscales_dev);
   if (rc != SVDQ_OK) {
@@ -450,9 +487,9 @@ int svdq_linear_plan_submit(svdq_linear_plan* p, const void* x_host, void* y_hos
   bad = bad || cudaStreamWaitEvent(p->s_run, q.x_ready, 0) != cudaSuccess;
   bad = bad || cudaStreamWaitEvent(p->s_run, q.y_done, 0) != cudaSuccess;
   if (bad) return SVDQ_ERR_CUDA;
-  rc = svdq_quantize_w4a4_act_fuse_lora(q.x, p->lora_down, p->smooth, p->smooth_table, q.act, q.ascales, q.lora_act,
-                                        q.ascales_swz, q.lora_act16, M, p->K, p->R, M_pad, p->dtype, SVDQ_QUANT_AUTO,
-                                        p->s_run);
+  rc = svdq_quantize_w4a4_act_fuse_lora_ws(q.x, p->lora_down, p->smooth, p->smooth_table, q.act, q.ascales, q.lora_act,
+                                           q.ascales_swz, q.lora_act16, M, p->K, p->R, M_pad, p->dtype, SVDQ_QUANT_AUTO,
+                                           p->quant_ws, p->quant_ws_bytes, p->s_run);
   if (rc != SVDQ_OK) return rc;
   rc = svdq_gemm_w4a4_ws(q.act, p->wgt, q.ascales_swz, p->wscales_swz, p->R > 0 ? q.lora_act16 : nullptr,
                          p->R > 0 ? p->lora_up : nullptr, p->R > 0 ? p->lora_up_f16 : nullptr, p->wc, p->bias, q.y, M_pad,
@@ -502,7 +539,7 @@ void svdq_linear_plan_destroy(svdq_linear_plan* p) {
     if (q.y_done != nullptr) cudaEventDestroy(q.y_done);
   }
   void* dev[] = {p->wgt, p->wscales_swz, p->lora_down, p->lora_up, p->lora_up_f16, p->smooth, p->smooth_table, p->wc, p->bias,
-                 p->split_ws};
+                 p->split_ws, p->quant_ws};
   for (void* d : dev)
     if (d != nullptr) cudaFree(d);
   if (p->s_in != nullptr) cudaStreamDestroy(p->s_in);

@@ -3,5 +3,6 @@
 #include "tensormap.cu"
 #include "quantize_generic.cu"
 #include "quantize_fused.cu"
+#include "quantize_stream.cu"
 #include "gemm_w4a4.cu"
 #include "capi.cu"

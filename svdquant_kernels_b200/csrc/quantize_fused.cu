@@ -46,6 +46,7 @@
 // outside [2^-60, 2^60] (2^16 for bf16) and the kernel then divides with __fdiv_rn.  amax / 6
 // uses the same three-step form (checked exhaustively as well).
 #include "nvfp4_math.cuh"
+#include "quantize_math.cuh"
 #include "sm100.cuh"
 #include "svdq_internal.h"
 
@@ -71,13 +72,13 @@ template <int RP>
 struct Cfg {
   static constexpr int W_BYTES = SLAB_K * RP * 2;                 // lora_down slab
   static constexpr int STAGE_BYTES = X_BYTES + W_BYTES + 1024;   // table slab + padding to the 1 KB the swizzled tiles need
-  static constexpr int STAGES_RAW = (232448 - 1024 - 512) / STAGE_BYTES;
+  static constexpr int STAGES_RAW = (232448 - 1024 - 512 - 1024) / STAGE_BYTES;
   // A multiple of the group count: a group then always meets the same stages, and the slab it waits
   // for is the direct successor (in that stage) of one it consumed itself.  A one-bit phase parity
   // cannot tell "one revolution behind" from "one ahead"; this rule makes the second impossible.
   static constexpr int STAGES = STAGES_RAW > 12 ? 12 : (STAGES_RAW / QUANT_GROUPS) * QUANT_GROUPS;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512;
+  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + 1024;   // ring, barriers, scale-constant table
   static constexpr int TMEM_COLS = RP < 32 ? 32 : RP;             // power of two >= 32
   static constexpr int EPI_COLS = RP / 4 < 32 ? 32 : RP / 4;      // accumulator columns per epilogue warp
   static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the ring");
@@ -85,7 +86,7 @@ struct Cfg {
 };
 
 struct Params {
-  const float2* table;    // [K] {smooth, 1/smooth} followed by one flag word, or null (no smoothing)
+  const float2* table;    // [K/2] {-s0, -s1, 1/s0, 1/s1} followed by one flag word, or null (no smoothing)
   uint8_t* act;           // [M_pad, K/2]
   uint8_t* scales;        // [K/16, M_pad]
   uint8_t* scales_swz;    // atom order or null
@@ -94,130 +95,15 @@ struct Params {
   int M, K, R, M_pad;
 };
 
-// Widen a pair of 16-bit values.  CANON adds +0 first, which turns -0 into +0 and changes nothing else
-// (the reference gives a zero the sign bit only when the value tests < 0).  The smoothing divide of
-// the fast path does the same by itself - for s > 0, q0 = x r keeps the zero's sign, e =
-// fma(-s, q0, x) is +0 and q = fma(e, r, q0) = +0 for either zero - so only the other paths ask
-// for it.
-template <typename T, bool CANON> __device__ __forceinline__ float2 unpack2(uint32_t v);
-template <> __device__ __forceinline__ float2 unpack2<__half, true>(uint32_t v) {
-  return __half22float2(__hadd2(*reinterpret_cast<__half2*>(&v), __float2half2_rn(0.0f)));
-}
-template <> __device__ __forceinline__ float2 unpack2<__half, false>(uint32_t v) {
-  return __half22float2(*reinterpret_cast<__half2*>(&v));
-}
-template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16, true>(uint32_t v) {
-  const __nv_bfloat162 c = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&v), __float2bfloat162_rn(0.0f));
-  const uint32_t u = *reinterpret_cast<const uint32_t*>(&c);
-  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
-}
-template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16, false>(uint32_t v) {
-  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
-}
-
 // float4 slot of (row, c4) in the partial-accumulator buffer; the XOR spreads the
 // rows a warp writes at once over all bank groups.
 __device__ __forceinline__ uint32_t partial_slot(uint32_t row, uint32_t c4, uint32_t rp4) {
   return row * rp4 + (c4 ^ (row & 7u));
 }
 
-template <typename T, bool CANON>
-__device__ __forceinline__ void unpack_group(const uint4& lo16, const uint4& hi16, float (&f)[16]) {
-  const uint32_t w[8] = {lo16.x, lo16.y, lo16.z, lo16.w, hi16.x, hi16.y, hi16.z, hi16.w};
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    const float2 v = unpack2<T, CANON>(w[j]);
-    f[2 * j] = v.x; f[2 * j + 1] = v.y;
-  }
-}
-
-// Two floats -> two E2M1 codes in one byte (hi in bits 7-4, lo in bits 3-0), round to nearest, saturating.
-__device__ __forceinline__ uint32_t cvt_e2m1x2(float hi, float lo) {
-  uint32_t d;
-  asm("{\n\t.reg .b8 r;\n\tcvt.rn.satfinite.e2m1x2.f32 r, %1, %2;\n\tcvt.u32.u8 %0, r;\n\t}" : "=r"(d) : "f"(hi), "f"(lo));
-  return d;
-}
-
-// Smoothing divide of one 16-element group (already widened to fp32); tb points at the group's
-// eight {s0, r0, s1, r1} table entries in shared memory (the same address in every lane).
-__device__ __forceinline__ void smooth_divide(float (&f)[16], const float4* tb, bool use_fdiv) {
-  if (!use_fdiv) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float4 t = tb[j];          // {s0, r0, s1, r1}
-      const float q0 = f[2 * j] * t.y;
-      f[2 * j] = fmaf(fmaf(-t.x, q0, f[2 * j]), t.y, q0);
-      const float q1 = f[2 * j + 1] * t.w;
-      f[2 * j + 1] = fmaf(fmaf(-t.z, q1, f[2 * j + 1]), t.w, q1);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float4 t = tb[j];
-      f[2 * j] = __fadd_rn(__fdiv_rn(f[2 * j], t.x), 0.0f);           // an underflow to -0 counts as +0
-      f[2 * j + 1] = __fadd_rn(__fdiv_rn(f[2 * j + 1], t.z), 0.0f);
-    }
-  }
-}
-
-// One 16-element group (smoothed, fp32): amax, scale byte, eight code bytes.
-__device__ __forceinline__ void quantize_group(float (&f)[16],
-                                               uint32_t& code_lo, uint32_t& code_hi, uint32_t& sbyte) {
-  float m0 = fmaxf(fabsf(f[0]), fabsf(f[1])), m1 = fmaxf(fabsf(f[2]), fabsf(f[3]));
-  float m2 = fmaxf(fabsf(f[4]), fabsf(f[5])), m3 = fmaxf(fabsf(f[6]), fabsf(f[7]));
-#pragma unroll
-  for (int j = 8; j < 16; j += 4) {
-    m0 = fmaxf(m0, fabsf(f[j])); m1 = fmaxf(m1, fabsf(f[j + 1]));
-    m2 = fmaxf(m2, fabsf(f[j + 2])); m3 = fmaxf(m3, fabsf(f[j + 3]));
-  }
-  const float amax = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-  // amax / 6, correctly rounded (amax is finite and >= 0; tiny quotients are clamped away below)
-  const float r6 = 0.16666667163372039794921875f;   // RN(1/6)
-  const float s0 = amax * r6;
-  float s = fmaf(fmaf(-6.0f, s0, amax), r6, s0);
-  s = fminf(fmaxf(s, 1e-12f), 448.0f);
-  const uint32_t sb = static_cast<uint32_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3));
-  sbyte = sb;
-  uint32_t lo = 0, hi = 0;
-  if (sb != 0u && sb != 0x7Eu) {
-    // Main path.  scale = J * 2^E with J in 1..15, so with t = 4 |v| / 2^E (an exact power-of-two
-    // scaling) the code is the number of n in {1,3,5,7,10,14,20} with n J <= t, i.e. with
-    // n J <= m = floor(t).  m / (4 J) then lies
-    // on a bound n/4 exactly when m = n J and is at least 1/(4 J) away from every bound otherwise,
-    // so m * RN(1/(4 J)) * (1 + 2^-20) is strictly above the bound in the first case and on the
-    // right side of it in the second, and the hardware's float -> E2M1 conversion (round to
-    // nearest, saturating) of that product returns exactly the reference's code; checked
-    // exhaustively over J and m.  The conversion also carries the sign and packs two codes.
-    const uint32_t e = sb >> 3, m3 = sb & 7u;
-    const uint32_t J = e ? 8u + m3 : m3;
-    const float mult = __uint_as_float((e ? 139u - e : 138u) << 23);      // 2^(2 - E)
-    const float rj = __fmul_rn(__frcp_rn(static_cast<float>(4u * J)), 1.00000095367431640625f);
-    uint32_t b[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      // m = trunc(4 v / 2^E) keeps the sign of v (also as -0 for a small negative v, whose code is
-      // "negative zero" in the reference too; v itself is never -0 here: inputs were made +0 and
-      // quotients cannot underflow in this path)
-      const float w0 = __fmul_rn(truncf(f[2 * j] * mult), rj);
-      const float w1 = __fmul_rn(truncf(f[2 * j + 1] * mult), rj);
-      b[j] = cvt_e2m1x2(w1, w0);     // low nibble = even element
-    }
-    lo = b[0] | (b[1] << 8) | (b[2] << 16) | (b[3] << 24);
-    hi = b[4] | (b[5] << 8) | (b[6] << 16) | (b[7] << 24);
-  } else {
-    // zero scale (everything non-zero saturates) or the 448 clamp (ratios are unbounded): compare path
-    float sf = e4m3_to_f32(static_cast<uint8_t>(sb));
-    sf = (sf == 0.0f) ? __uint_as_float(4u) : sf;     // 2^-147 * {.25 .. 5}: positive, below any normal number
-    GroupBounds gb;
-    gb.p[0] = sf * 0.25f; gb.p[1] = sf * 0.75f; gb.p[2] = sf * 1.25f; gb.p[3] = sf * 1.75f;
-    gb.p[4] = sf * 2.5f;  gb.p[5] = sf * 3.5f;  gb.p[6] = sf * 5.0f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) lo += e2m1_code(f[j], gb) << (4 * j);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) hi += e2m1_code(f[8 + j], gb) << (4 * j);
-  }
-  code_lo = lo; code_hi = hi;
-}
+using qmath::quantize_group;
+using qmath::smooth_divide;
+using qmath::unpack_group;
 
 template <typename T, int RP>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -236,6 +122,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* lora_unfit = tmem_slot + 2;        // bf16 form: some LoRA value this CTA wrote does not fit fp16
+  float2* scale_lut = reinterpret_cast<float2*>(smem + C::RING_BYTES + 512);   // per scale byte: {2^(2-E), ~1/(4J)}
   const WaitCtx ctx{abort_flag};
 
   // warp index through a shuffle: provably warp-uniform, so the role branches are convergent code
@@ -269,6 +156,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     tmem_alloc(tmem_slot, C::TMEM_COLS);
     tmem_relinquish();
   }
+  qmath::fill_scale_lut(scale_lut, threadIdx.x, NUM_THREADS);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -353,7 +241,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         raw[rr][0] = *reinterpret_cast<const uint4*>(xrow + (((2 * g) ^ (row & 7)) << 4));
         raw[rr][1] = *reinterpret_cast<const uint4*>(xrow + (((2 * g + 1) ^ (row & 7)) << 4));
       }
-      float f[2][16];
+      float2 f[2][8];
       if (has_table && !use_fdiv) {
         unpack_group<T, false>(raw[0][0], raw[0][1], f[0]);
         unpack_group<T, false>(raw[1][0], raw[1][1], f[1]);
@@ -381,7 +269,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       for (int rr = 0; rr < 2; ++rr) {
         const int row = row_base + 8 * rr;
         uint32_t clo, chi, sb;
-        quantize_group(f[rr], clo, chi, sb);
+        quantize_group(f[rr], scale_lut, clo, chi, sb);
         *reinterpret_cast<uint2*>(act_base + static_cast<size_t>(row) * (p.K >> 1) + (k0 >> 1)) = make_uint2(clo, chi);
         p.scales[static_cast<size_t>(gi) * p.M_pad + m0 + row] = static_cast<uint8_t>(sb);
         if (p.scales_swz != nullptr) p.scales_swz[sf_swizzled_offset(m0 + row, gi, groups)] = static_cast<uint8_t>(sb);
@@ -491,7 +379,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   }
 }
 
-// {smooth, 1/smooth} per column, then one flag word: 1 if any smooth value lies outside
+// Per column pair {-s0, -s1, 1/s0, 1/s1}, then one flag word: 1 if any smooth value lies outside
 // [2^-60, 2^60] (2^16 for bf16; negative, zero and NaN count as outside), where the three-step divide
 // could over- or underflow or leave a zero with the wrong sign.
 template <typename T>
@@ -502,10 +390,11 @@ __global__ void smooth_table_kernel(const T* __restrict__ smooth, float2* __rest
   __shared__ int bad;
   if (threadIdx.x == 0) bad = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < K; i += blockDim.x) {
-    const float s = to_f32(smooth[i]);
-    table[i] = make_float2(s, __frcp_rn(s));
-    if (!(s >= 8.6736174e-19f && s <= kMaxSmooth)) bad = 1;      // also: negative, zero or NaN
+  float4* pairs = reinterpret_cast<float4*>(table);
+  for (int i = threadIdx.x; i < K / 2; i += blockDim.x) {
+    const float s0 = to_f32(smooth[2 * i]), s1 = to_f32(smooth[2 * i + 1]);
+    pairs[i] = make_float4(-s0, -s1, __frcp_rn(s0), __frcp_rn(s1));
+    if (!(s0 >= 8.6736174e-19f && s0 <= kMaxSmooth) || !(s1 >= 8.6736174e-19f && s1 <= kMaxSmooth)) bad = 1;
   }
   __syncthreads();
   if (threadIdx.x == 0) *reinterpret_cast<uint2*>(table + K) = make_uint2(bad ? 1u : 0u, 0u);

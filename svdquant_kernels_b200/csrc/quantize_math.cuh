@@ -1,0 +1,162 @@
+// Per-group arithmetic of the activation quantizer, shared by both fused kernels.
+//
+// Results follow baseline/kernels/quantize_w4a4_act_fuse_lora/ref.py:40-48 and
+// baseline/kernels/_nvfp4.py:27-41, :82-91 of the reference bit for bit; none of it
+// runs a per-element IEEE divide.  Two fp32 lanes at a time where the hardware has
+// a packed instruction (mul / fma on f32x2), three-input |max| for the group amax,
+// and a 128-entry table in shared memory for the two constants that depend on the
+// scale byte.
+//
+// Smoothing divide.  x / s must equal the IEEE quotient: q0 = x*r, e = fma(-s, q0, x),
+// q = fma(e, r, q0) with r = RN(1/s) is the correctly rounded quotient for operands of
+// at most 11 significant bits as long as nothing over- or underflows (checked
+// exhaustively over mantissas on the CPU).  The table therefore holds, per column
+// pair, {-s0, -s1, r0, r1}, and a flag word behind it says whether some s lies outside
+// the safe range, in which case the kernels divide with __fdiv_rn.
+//
+// Codes.  The scale byte is J * 2^E (J = 1..15), so m = trunc(4 v / 2^E) is an integer
+// with v's sign and the E2M1 code is the number of n in {1,3,5,7,10,14,20} with
+// n J <= |m|.  m / (4 J) lies on a rounding bound of E2M1 exactly when |m| = n J and at
+// least 1/(4 J) away from every bound otherwise, so RN(m * RN(1/(4 J)) * (1 + 2^-20))
+// is strictly above the bound in the first case and on the right side of it in the
+// second, and the hardware conversion cvt.rn.satfinite.e2m1x2.f32 of it returns the
+// reference's code, sign included (checked exhaustively over J and m on the CPU).
+// Groups whose scale byte is 0 (everything non-zero saturates) or the 448 clamp
+// (ratios are unbounded) compare against the seven exact products instead.
+#pragma once
+
+#include "nvfp4_math.cuh"
+
+namespace svdq {
+namespace qmath {
+
+// Widen a pair of 16-bit values.  CANON adds +0 first, which turns -0 into +0 and changes nothing
+// else (the reference gives a zero the sign bit only when the value tests < 0).  The smoothing
+// divide of the fast path does the same by itself - for s > 0, q0 = x r keeps the zero's sign,
+// e = fma(-s, q0, x) is +0 and q = fma(e, r, q0) = +0 for either zero - so only the other paths
+// ask for it.
+template <typename T, bool CANON> __device__ __forceinline__ float2 unpack2(uint32_t v);
+template <> __device__ __forceinline__ float2 unpack2<__half, true>(uint32_t v) {
+  return __half22float2(__hadd2(*reinterpret_cast<__half2*>(&v), __float2half2_rn(0.0f)));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half, false>(uint32_t v) {
+  return __half22float2(*reinterpret_cast<__half2*>(&v));
+}
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16, true>(uint32_t v) {
+  const __nv_bfloat162 c = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&v), __float2bfloat162_rn(0.0f));
+  const uint32_t u = *reinterpret_cast<const uint32_t*>(&c);
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16, false>(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+}
+
+template <typename T, bool CANON>
+__device__ __forceinline__ void unpack_group(const uint4& lo16, const uint4& hi16, float2 (&f)[8]) {
+  const uint32_t w[8] = {lo16.x, lo16.y, lo16.z, lo16.w, hi16.x, hi16.y, hi16.z, hi16.w};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) f[j] = unpack2<T, CANON>(w[j]);
+}
+
+// Smoothing divide of one 16-element group; tb points at the group's eight
+// {-s0, -s1, r0, r1} table entries in shared memory (the same address in every lane of a quad column).
+__device__ __forceinline__ void smooth_divide(float2 (&f)[8], const float4* tb, bool use_fdiv) {
+  if (!use_fdiv) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 t = tb[j];
+      const float2 ns = make_float2(t.x, t.y), r = make_float2(t.z, t.w);
+      const float2 q0 = __fmul2_rn(f[j], r);
+      f[j] = __ffma2_rn(__ffma2_rn(ns, q0, f[j]), r, q0);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 t = tb[j];
+      f[j].x = __fadd_rn(__fdiv_rn(f[j].x, -t.x), 0.0f);           // an underflow to -0 counts as +0
+      f[j].y = __fadd_rn(__fdiv_rn(f[j].y, -t.y), 0.0f);
+    }
+  }
+}
+
+// {2^(2-E), RN(1/(4 J)) (1 + 2^-20)} of scale byte sb = J 2^E; {0, 0} for the two bytes that take the compare path
+__device__ __forceinline__ float2 scale_constants(uint32_t sb) {
+  if (sb == 0u || sb >= 0x7Eu) return make_float2(0.0f, 0.0f);
+  const uint32_t e = sb >> 3, m3 = sb & 7u;
+  const uint32_t J = e ? 8u + m3 : m3;
+  const float mult = __uint_as_float((e ? 139u - e : 138u) << 23);
+  const float rj = __fmul_rn(__frcp_rn(static_cast<float>(4u * J)), 1.00000095367431640625f);
+  return make_float2(mult, rj);
+}
+constexpr int kScaleLutEntries = 128;
+__device__ __forceinline__ void fill_scale_lut(float2* lut, int tid, int nthreads) {
+  for (int i = tid; i < kScaleLutEntries; i += nthreads) lut[i] = scale_constants(static_cast<uint32_t>(i));
+}
+
+__device__ __forceinline__ float max3abs(float a, float b, float c) {
+  float r;
+  asm("max.abs.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// Four pairs of floats -> eight E2M1 codes in one word (element 2j in bits 8j..8j+3, element 2j+1
+// above it), round to nearest, saturating, sign included.
+__device__ __forceinline__ uint32_t cvt_e2m1x8(float2 a, float2 b, float2 c, float2 d) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 q0, q1, q2, q3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 q0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 q1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 q2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 q3, %8, %7;\n\t"
+      "mov.b32 %0, {q0, q1, q2, q3};\n\t}"
+      : "=r"(r)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y), "f"(d.x), "f"(d.y));
+  return r;
+}
+
+// One 16-element group (smoothed, fp32): amax, scale byte, eight code bytes.
+__device__ __forceinline__ void quantize_group(float2 (&f)[8], const float2* scale_lut,
+                                               uint32_t& code_lo, uint32_t& code_hi, uint32_t& sbyte) {
+  const float m0 = max3abs(f[0].x, f[0].y, f[1].x), m1 = max3abs(f[1].y, f[2].x, f[2].y);
+  const float m2 = max3abs(f[3].x, f[3].y, f[4].x), m3 = max3abs(f[4].y, f[5].x, f[5].y);
+  const float m4 = max3abs(f[6].x, f[6].y, f[7].x);
+  const float amax = fmaxf(max3abs(m0, m1, m2), max3abs(m3, m4, f[7].y));
+  // amax / 6, correctly rounded (amax is finite and >= 0; tiny quotients are clamped away below)
+  const float r6 = 0.16666667163372039794921875f;   // RN(1/6)
+  const float s0 = amax * r6;
+  float s = fmaf(fmaf(-6.0f, s0, amax), r6, s0);
+  s = fminf(fmaxf(s, 1e-12f), 448.0f);
+  const uint32_t sb = static_cast<uint32_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3));
+  sbyte = sb;
+  const float2 k = scale_lut[sb];
+  if (k.x != 0.0f) {
+    // m = trunc(4 v / 2^E) keeps the sign of v (also as -0 for a small negative v, whose code is
+    // "negative zero" in the reference too; v itself is never -0 here: inputs were made +0 and
+    // quotients cannot underflow in this path)
+    const float2 mult = make_float2(k.x, k.x), rj = make_float2(k.y, k.y);
+    float2 w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float2 t = __fmul2_rn(f[j], mult);
+      w[j] = __fmul2_rn(make_float2(truncf(t.x), truncf(t.y)), rj);
+    }
+    code_lo = cvt_e2m1x8(w[0], w[1], w[2], w[3]);
+    code_hi = cvt_e2m1x8(w[4], w[5], w[6], w[7]);
+  } else {
+    // zero scale (everything non-zero saturates) or the 448 clamp (ratios are unbounded): compare path
+    float sf = e4m3_to_f32(static_cast<uint8_t>(sb));
+    sf = (sf == 0.0f) ? __uint_as_float(4u) : sf;     // 2^-147 * {.25 .. 5}: positive, below any normal number
+    GroupBounds gb;
+    gb.p[0] = sf * 0.25f; gb.p[1] = sf * 0.75f; gb.p[2] = sf * 1.25f; gb.p[3] = sf * 1.75f;
+    gb.p[4] = sf * 2.5f;  gb.p[5] = sf * 3.5f;  gb.p[6] = sf * 5.0f;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) lo += (e2m1_code(f[j].x, gb) << (8 * j)) + (e2m1_code(f[j].y, gb) << (8 * j + 4));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) hi += (e2m1_code(f[4 + j].x, gb) << (8 * j)) + (e2m1_code(f[4 + j].y, gb) << (8 * j + 4));
+    code_lo = lo; code_hi = hi;
+  }
+}
+
+}  // namespace qmath
+}  // namespace svdq

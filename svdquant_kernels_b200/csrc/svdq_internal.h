@@ -26,6 +26,13 @@ int launch_quantize_fused(const void* x, const void* lora_down, const void* smoo
 
 int quantize_fused_max_clusters(int R, int ks, int dtype);
 
+// quantize_stream.cu : the form for tall activations (128- or 256-row tiles, K split met in a workspace)
+bool quantize_stream_plan(int M, int K, int R, int M_pad, int* tm_out, int* ks_out);
+size_t quantize_stream_workspace_bytes(int M, int K, int R, int M_pad);
+int launch_quantize_stream(const void* x, const void* lora_down, const void* smooth_table, void* act, void* ascales,
+                           float* lora_act, void* ascales_swz, void* lora_act16, int M, int K, int R, int M_pad,
+                           int dtype, void* ws, size_t ws_bytes, int tm, int ks, cudaStream_t stream);
+
 // gemm_w4a4.cu
 bool gemm_supported(int M, int N, int K, int R);
 // Column-sharded form: y is the local [M, y_ld] matrix, this launch fills columns [col0, col0 + N)

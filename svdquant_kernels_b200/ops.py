@@ -167,10 +167,19 @@ def quantize_w4a4_act_fuse_lora(
     # and the per-32-row "fits fp16" words (a flat buffer, see include/svdq_b200.h)
     if R > 0 and la16 is None:
         la16 = torch.empty(_la16_elems(M_pad, R, input.dtype), dtype=input.dtype, device=dev)
+    # the streaming form (on request) lets its K ranks meet in a workspace, cached per device and stream
+    ws = None
+    if _force >= _lib.QUANT_FORCE_STREAM:
+        ws = _workspace(_QUANT_WS, dev, _QUANT_WS_FORCED, 2048)
     with _on_device(dev):
-        rc = lib.svdq_quantize_w4a4_act_fuse_lora(
-            _ptr(x), _ptr(ld), _ptr(sm), _ptr(table), _ptr(act), _ptr(ascales), _ptr(lora_act), _ptr(swz), _ptr(la16),
-            M, K, R, M_pad, _DT[input.dtype], _force, _stream(dev))
+        if ws is not None:
+            rc = lib.svdq_quantize_w4a4_act_fuse_lora_ws(
+                _ptr(x), _ptr(ld), _ptr(sm), _ptr(table), _ptr(act), _ptr(ascales), _ptr(lora_act), _ptr(swz), _ptr(la16),
+                M, K, R, M_pad, _DT[input.dtype], _force, _ptr(ws), ws.numel(), _stream(dev))
+        else:
+            rc = lib.svdq_quantize_w4a4_act_fuse_lora(
+                _ptr(x), _ptr(ld), _ptr(sm), _ptr(table), _ptr(act), _ptr(ascales), _ptr(lora_act), _ptr(swz), _ptr(la16),
+                M, K, R, M_pad, _DT[input.dtype], _force, _stream(dev))
     _lib.check(rc, "quantize_w4a4_act_fuse_lora")
     if swz is not None:
         _attach(ascales, swz)
@@ -379,19 +388,43 @@ def gemm_w4a4(
     return y
 
 
-_SPLIT_WS: dict = {}
+_SPLIT_WS: dict = {}     # GEMM split-K workspaces
+_QUANT_WS: dict = {}     # quantizer (streaming form) workspaces
+_QUANT_WS_BYTES: dict = {}
+_QUANT_WS_FORCED = 2048 + 8 * 8192 * 512     # room for any forced split of up to 8192 padded rows
+
+
+def _workspace(table: dict, dev: torch.device, nbytes: int, head: int) -> torch.Tensor:
+    """Workspace of the current stream of `dev` (its first `head` bytes are counters, zeroed when it is
+    made; every completed call leaves them zero).  One per stream, because calls that share a
+    workspace must not overlap."""
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev))
+    ws = table.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 10 << 20), dtype=torch.uint8, device=dev)
+        ws[:head].zero_()                      # the counters; the partial sums need no initial value
+        table[key] = ws
+    return ws
 
 
 def _split_workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
-    """Split-K workspace of the current stream of `dev` (ticket counters zeroed when made; every call
-    leaves them zero).  One per stream, because calls that share a workspace must not overlap."""
-    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev))
-    ws = _SPLIT_WS.get(key)
-    if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 10 << 20), dtype=torch.uint8, device=dev)
-        ws[:1024].zero_()                      # the ticket counters; the partial tiles need no initial value
-        _SPLIT_WS[key] = ws
-    return ws
+    return _workspace(_SPLIT_WS, dev, nbytes, 1024)
+
+
+def _quant_ws_bytes(M: int, K: int, R: int, M_pad: int) -> int:
+    key = (M, K, R, M_pad)
+    n = _QUANT_WS_BYTES.get(key)
+    if n is None:
+        n = _QUANT_WS_BYTES[key] = int(_lib.load().svdq_quantize_workspace_bytes(M, K, R, M_pad))
+    return n
+
+
+def reset_workspaces() -> None:
+    """Forget the cached workspaces (new ones are made, with zeroed counters, on the next calls).  Call
+    this after `_lib.device_status()` reported a failure: a kernel that gave up on a bounded wait may
+    have left counters non-zero."""
+    _SPLIT_WS.clear()
+    _QUANT_WS.clear()
 
 
 launch_v2 = gemm_w4a4   # the reference's name for the same entry point

@@ -11,7 +11,7 @@ from oracle import nvfp4_oracle as O
 
 pytestmark = pytest.mark.gpu
 LORA_TOL = 1e-3
-GENERIC, FUSED = 1, 2
+GENERIC, FUSED, STREAM = 1, 2, 0x100000
 
 
 def _ops():
@@ -34,11 +34,14 @@ def _check(x, ld, sm, force, pad=256):
     M = x.shape[0]
     assert (lora[M:] == 0).all()
     # the twins the GEMM consumes
-    twin = getattr(ascales, "_svdq_twin", None)
-    if twin is not None:
-        assert (twin[0].cpu().numpy() == O.swizzle_scales(o_sc)).all(), "swizzled scales differ"
-    twin16 = getattr(lora, "_svdq_twin", None)
-    if twin16 is not None and ld.shape[1] > 0:
+    twin = ops._attached(ascales)
+    if act.shape[0] % 128 == 0 and (2 * act.shape[1]) % 64 == 0:
+        assert twin is not None, "the quantizer did not leave the tensor-core twin of the scales"
+        assert (twin.cpu().numpy() == O.swizzle_scales(o_sc)).all(), "swizzled scales differ"
+    twin16 = ops._attached(lora)
+    if ld.shape[1] > 0:
+        assert twin16 is not None, "the quantizer did not leave the 16-bit twin of lora_act"
+        twin16 = (twin16,)
         la = lora.cpu().numpy()
         want16 = O.f32_to_bits(np.clip(la, -65504.0, 65504.0), "fp16")
         if x.dtype == torch.float16:
@@ -56,7 +59,9 @@ def _check(x, ld, sm, force, pad=256):
             flags = flags[0::2] | (flags[1::2] << 16)
             blocks = -(-la.shape[0] // 32)
             unfit = np.array([not (np.abs(la[32 * b:32 * b + 32]) <= 65504.0).all() for b in range(blocks)])
-            if force == FUSED:
+            if force >= STREAM:
+                assert ((flags[:blocks] != 0) == unfit).all(), "fits-fp16 words of lora_act differ"
+            elif force == FUSED:
                 # a zero word promises that the 32 rows fit fp16; with few row tiles (more than two CTAs
                 # per tile) the kernel makes no promise, otherwise the words are exact
                 assert not ((flags[:blocks] == 0) & unfit).any(), "a row block that does not fit fp16 is marked as fitting"
@@ -103,6 +108,43 @@ def test_fused_matches_oracle(M, K, R, dtype):
     x, ld, sm = _inputs(M, K, R, dtype, 100 + M + K)
     _check(x, ld, sm, FUSED)
     _check(x, ld, None, FUSED)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,R,tm,ks", [(512, 512, 32, 128, 4), (512, 1024, 128, 256, 2), (1024, 1024, 64, 256, 8),
+                                         (300, 640, 16, 128, 2), (256, 256, 0, 128, 1), (700, 2560, 128, 256, 1),
+                                         (2000, 1536, 128, 128, 4), (2304, 960, 104, 256, 8), (256, 15360, 128, 256, 8),
+                                         (128, 7680, 8, 128, 4)])
+def test_stream_form_matches_oracle(M, K, R, tm, ks, dtype):
+    """The form for tall activations, with tile height and K split forced so that every combination runs
+    on small inputs: codes, scales and twins as in the cluster form, the K ranks' partial LoRA sums
+    met in the workspace (twice in a row: the counters must return to zero)."""
+    x, ld, sm = _inputs(M, K, R, dtype, 300 + M + K)
+    force = STREAM | (tm << 8) | (ks << 4)
+    _check(x, ld, sm, force)
+    _check(x, ld, None, force)
+    a, s, l = _check(x, ld, sm, force)
+    a2, s2, l2 = _ops().quantize_w4a4_act_fuse_lora(x, ld, sm)       # whatever form the library picks
+    torch.cuda.synchronize()
+    assert torch.equal(a, a2) and torch.equal(s.view(torch.uint8), s2.view(torch.uint8))
+    if R > 0:
+        assert O.rel_l2(l.cpu().numpy(), l2.cpu().numpy()) <= 1e-5
+
+
+def test_stream_form_full_size_and_deterministic():
+    """The benchmark shape in the planned streaming form (4352 x 3840, R = 128: 34 tiles x 4 or 17 x 8
+    CTAs) against the oracle, and ten runs of it give one lora_act: the K ranks are added in rank
+    order whatever order they arrive in."""
+    from svdquant_kernels_b200.workloads import CONFIGS, make_inputs
+    inp = make_inputs(CONFIGS["c1"])
+    x, ld, sm = inp.x.cuda(), inp.lora_down.cuda(), inp.smooth.cuda()
+    for force in (STREAM, STREAM | (256 << 8) | (8 << 4), STREAM | (128 << 8) | (4 << 4)):
+        _, _, first = _check(x, ld, sm, force)
+        for _ in range(9):
+            _, _, l = _ops().quantize_w4a4_act_fuse_lora(x, ld, sm, _force=force)
+            assert torch.equal(first, l)
+    torch.cuda.synchronize()
+    assert_device_clean()
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
