@@ -175,6 +175,26 @@ int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, co
                    void* y, int M, int N, int K, int R, int dtype, int variant, void* stream);
 
 /*
+ * svdq_gemm_w4a4 that also quantises its result for the next W4A4 linear, in the same epilogue:
+ * the optional smooth_next -> (qout, oscales) outputs of gemm_w4a4_ref
+ * (baseline/kernels/gemm_w4a4/ref.py:80-87; the reference's own GPU kernels dropped them,
+ * docs/architecture.md:78-99).  The fp32 result (after wcscales and bias, BEFORE the cast to the
+ * output type) is divided by smooth_next and packed with quantize_nvfp4_rows(pad_size = 1):
+ *   smooth_next [N]       f16/bf16 (the output type)
+ *   qout        [M, N/2]  u8, two E2M1 codes per byte
+ *   oscales     [N/16, M] u8, E4M3 bit patterns
+ *   oscales_swz optional, M*N/16 bytes: oscales in the tensor-core atom order (needs N % 64 == 0),
+ *               so that a following svdq_gemm_w4a4 can take (qout, oscales_swz) as its act / ascales_swz
+ * y is written as by svdq_gemm_w4a4.  Codes and scales equal the oracle's wherever the kernel's
+ * fp32 y equals the oracle's (both add the same products, in different orders).
+ * Plain tiles only: variants 0, 128, 256, 2128, 2256.
+ */
+int svdq_gemm_w4a4_next(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                        const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
+                        const void* bias, void* y, const void* smooth_next, void* qout, void* oscales, void* oscales_swz,
+                        int M, int N, int K, int R, int dtype, int variant, void* stream);
+
+/*
  * svdq_gemm_w4a4 with a caller-owned workspace in device memory, for problems with few output tiles
  * (a few hundred rows: the small-M shapes of GEMM_SHAPES in
  * cute_kernels/gemm_w4a4/harness.py:17-24, where the reference's kernels leave most SMs idle).

@@ -35,6 +35,7 @@ SIGNATURES = {
     "svdq_cast_lora_act": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "svdq_lora_up_to_f16": (c_int, [c_void_p, c_void_p, c_longlong]),
     "svdq_gemm_w4a4": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p]),
+    "svdq_gemm_w4a4_next": (c_int, [c_void_p] * 14 + [c_int] * 6 + [c_void_p]),
     "svdq_gemm_w4a4_workspace_bytes": (c_ulonglong, [c_int, c_int, c_int, c_int]),
     "svdq_gemm_w4a4_ws": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p, c_ulonglong, c_void_p]),
     "svdq_gemm_w4a4_static_ws": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_void_p]),

@@ -194,6 +194,28 @@ int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, co
                     dtype, variant, nullptr, 0, stream);
 }
 
+int svdq_gemm_w4a4_next(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
+                        const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
+                        const void* bias, void* y, const void* smooth_next, void* qout, void* oscales, void* oscales_swz,
+                        int M, int N, int K, int R, int dtype, int variant, void* stream) {
+  if (dtype != SVDQ_DTYPE_F16 && dtype != SVDQ_DTYPE_BF16) return SVDQ_ERR_DTYPE;
+  if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
+  if (act == nullptr || wgt == nullptr || ascales_swz == nullptr || wscales_swz == nullptr || y == nullptr ||
+      smooth_next == nullptr || qout == nullptr || oscales == nullptr)
+    return SVDQ_ERR_NULL;
+  if ((lora_act16 == nullptr) != (lora_up == nullptr)) return SVDQ_ERR_NULL;
+  if (R > 0 && lora_act16 == nullptr) return SVDQ_ERR_NULL;
+  if (lora_act16 == nullptr) R = 0;
+  if (!aligned16(act) || !aligned16(wgt) || !aligned16(ascales_swz) || !aligned16(wscales_swz) ||
+      !aligned16(lora_act16) || !aligned16(lora_up) || !aligned16(lora_up_f16) || !aligned16(y) || !aligned16(qout))
+    return SVDQ_ERR_ALIGN;
+  if (oscales_swz != nullptr && N % 64 != 0) return SVDQ_ERR_SHAPE;
+  GemmTp extra;
+  extra.smooth_next = smooth_next; extra.qout = qout; extra.oscales = oscales; extra.oscales_swz = oscales_swz;
+  return launch_gemm_w4a4(act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N,
+                          K, R, dtype, variant, extra, static_cast<cudaStream_t>(stream));
+}
+
 unsigned long long svdq_gemm_w4a4_workspace_bytes(int M, int N, int K, int R) {
   return static_cast<unsigned long long>(gemm_split_workspace_bytes(M, N, K, R));
 }

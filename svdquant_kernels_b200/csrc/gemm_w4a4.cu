@@ -63,6 +63,7 @@
 // the result does not depend on who finished first - runs the epilogue and zeroes the counter.
 // No CTA waits for another, so nothing depends on the CTAs of a tile running together.
 #include "nvfp4_math.cuh"
+#include "quantize_math.cuh"
 #include "sm100.cuh"
 #include "svdq_internal.h"
 
@@ -96,7 +97,7 @@ struct Cfg {
   static constexpr int GROUPS_PER_WARP = BN / 128;                 // 64-column strips each epilogue warp handles per tile
   static constexpr int STORE_BUFS = 1;
   static constexpr int STORE_BYTES = EPI_WARPS * STORE_BUFS * STORE_BUF_BYTES;
-  static constexpr int TAIL_BYTES = 2048 /*affine*/ + 512 /*barriers*/;
+  static constexpr int TAIL_BYTES = 3072 /*affine: wcscales, bias, smooth_next*/ + 512 /*barriers*/;
   static constexpr int STAGES_RAW = (232448 - 1024 - STORE_BYTES - TAIL_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SFA_COLS = 16;                 // 4 k-blocks x 4 columns
@@ -133,6 +134,12 @@ struct Params {
   int splits;
   float4* ws_partials;
   unsigned int* ws_tickets;
+  // Next-layer quantisation (NEXT kernels only): the fp32 result, before its cast, divided by
+  // smooth_next [N] and packed as NVFP4 rows: qout [M, N/2], oscales [N/16, M] (+ the tensor-core twin).
+  const void* smooth_next;
+  uint8_t* qout;
+  uint8_t* oscales;
+  uint8_t* oscales_swz;
 };
 
 __device__ __forceinline__ uint32_t pack2(__half a, __half b) {
@@ -159,7 +166,7 @@ template <typename T> __device__ __forceinline__ float as_f32(T v);
 template <> __device__ __forceinline__ float as_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float as_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
-template <int CG, int BN, typename OutT, bool SK = false>
+template <int CG, int BN, typename OutT, bool SK = false, bool NEXT = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmLA, const __grid_constant__ CUtensorMap tmLU,
@@ -175,8 +182,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* store_bufs = smem + C::STAGES * C::STAGE_BYTES;        // 1024-aligned: every stage is a multiple of 1 KB
   uint8_t* tail = store_bufs + C::STORE_BYTES;
-  float* affine = reinterpret_cast<float*>(tail);                 // [2][BN] : wcscales, bias of the current tile
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 2048);
+  float* affine = reinterpret_cast<float*>(tail);                 // [3][BN] : wcscales, bias, smooth_next of the current tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 3072);
   uint64_t* full = bars;                                          // [STAGES]     A / B (or LoRA) operands landed (leader CTA's copy is used)
   uint64_t* empty = bars + C::STAGES;                             // [STAGES]     stage consumed by the MMAs (per CTA)
   uint64_t* full_sf = bars + 2 * C::STAGES;                       // [STAGES]     the stage's scale atoms landed (leader's copy)
@@ -432,6 +439,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int c = threadIdx.x; c < BN; c += EPI_WARPS * 32) {
         affine[c] = wc != nullptr ? as_f32<OutT>(wc[n0 + c]) : 1.0f;
         affine[BN + c] = bias != nullptr ? as_f32<OutT>(bias[n0 + c]) : 0.0f;
+        if constexpr (NEXT) affine[2 * BN + c] = as_f32<OutT>(static_cast<const OutT*>(p.smooth_next)[n0 + c]);
       }
       asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
       if (!mbar_wait(&acc_full[as], aph, ctx, kDevWaitAcc, tcount)) ok = false;
@@ -519,6 +527,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const float4* wc4 = reinterpret_cast<const float4*>(affine + cbase + hc * 32);
           const float4* bs4 = reinterpret_cast<const float4*>(affine + BN + cbase + hc * 32);
           uint32_t o[16];
+          [[maybe_unused]] float2 qf[8];      // NEXT: the 16 values of the current column group, divided by smooth_next
+          [[maybe_unused]] uint32_t qcodes[4], qscales[2];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             float a0 = __uint_as_float(v[g][hc][4 * i]), a1 = __uint_as_float(v[g][hc][4 * i + 1]);
@@ -533,6 +543,30 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
             o[2 * i] = pack2f<OutT>(a0, a1);
             o[2 * i + 1] = pack2f<OutT>(a2, a3);
+            if constexpr (NEXT) {
+              // IEEE divide of the uncast fp32 value, as the reference does; + 0 turns a -0 quotient into
+              // +0 (the reference gives a zero the sign bit only when the value tests < 0)
+              const float4 s4 = reinterpret_cast<const float4*>(affine + 2 * BN + cbase + hc * 32)[i];
+              qf[2 * (i & 3)] = make_float2(__fadd_rn(__fdiv_rn(a0, s4.x), 0.0f), __fadd_rn(__fdiv_rn(a1, s4.y), 0.0f));
+              qf[2 * (i & 3) + 1] = make_float2(__fadd_rn(__fdiv_rn(a2, s4.z), 0.0f), __fadd_rn(__fdiv_rn(a3, s4.w), 0.0f));
+              if ((i & 3) == 3)
+                qmath::quantize_group(qf, nullptr, qcodes[2 * (i >> 2)], qcodes[2 * (i >> 2) + 1], qscales[i >> 2]);
+            }
+          }
+          if constexpr (NEXT) {
+            if (ok) {
+              // this thread's row: 32 columns = 16 code bytes and two scale bytes
+              const uint32_t row = static_cast<uint32_t>(m0 + quarter * 32 + lane);
+              const uint32_t col = static_cast<uint32_t>(n0 + cbase + hc * 32);
+              *reinterpret_cast<uint4*>(p.qout + static_cast<size_t>(row) * (p.N >> 1) + (col >> 1)) =
+                  make_uint4(qcodes[0], qcodes[1], qcodes[2], qcodes[3]);
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const uint32_t gcol = (col >> 4) + h;
+                p.oscales[static_cast<size_t>(gcol) * p.M + row] = static_cast<uint8_t>(qscales[h]);
+                if (p.oscales_swz != nullptr) p.oscales_swz[sf_swizzled_offset(row, gcol, p.N >> 4)] = static_cast<uint8_t>(qscales[h]);
+              }
+            }
           }
           // row `lane` of the strip: 16-byte chunks hc*4 .. hc*4+3, XOR-swizzled like the TMA box
 #pragma unroll
@@ -603,7 +637,7 @@ bool gemm_supported(int M, int N, int K, int R) {
   return M > 0 && N > 0 && K > 0 && M % 128 == 0 && N % 128 == 0 && K % 64 == 0 && R >= 0 && R % 16 == 0;
 }
 
-template <int CG, int BN, typename OutT, bool SK = false>
+template <int CG, int BN, typename OutT, bool SK = false, bool NEXT = false>
 static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, const void* sfb, const void* la,
                          const void* lu, const void* lu_f16, const void* wc, const void* bias, void* y, int M, int N,
                          int K, int R, const GemmTp& tp, cudaStream_t stream, int splits = 1) {
@@ -644,7 +678,11 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   p.splits = SK ? splits : 1;
   p.ws_tickets = static_cast<unsigned int*>(tp.ws);
   p.ws_partials = tp.ws != nullptr ? reinterpret_cast<float4*>(static_cast<uint8_t*>(tp.ws) + kSplitTicketBytes) : nullptr;
-  auto kern = gemm::gemm_w4a4_kernel<CG, BN, OutT, SK>;
+  p.smooth_next = tp.smooth_next;
+  p.qout = static_cast<uint8_t*>(tp.qout);
+  p.oscales = static_cast<uint8_t*>(tp.oscales);
+  p.oscales_swz = static_cast<uint8_t*>(tp.oscales_swz);
+  auto kern = gemm::gemm_w4a4_kernel<CG, BN, OutT, SK, NEXT>;
   // the attribute is per device: remember which devices of this process have it
   static bool configured[64] = {};
   int dev = 0;
@@ -672,14 +710,14 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   return SVDQ_OK;
 }
 
-template <typename OutT>
+template <typename OutT, bool NEXT>
 static int launch_gemm_dt(int cg, int bn, const void* act, const void* wgt, const void* sfa, const void* sfb,
                           const void* la, const void* lu, const void* lu_f16, const void* wc, const void* bias, void* y,
                           int M, int N, int K, int R, const GemmTp& tp, cudaStream_t stream) {
-  if (cg == 2 && bn == 256) return launch_gemm_t<2, 256, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
-  if (cg == 2 && bn == 128) return launch_gemm_t<2, 128, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
-  if (cg == 1 && bn == 256) return launch_gemm_t<1, 256, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
-  return launch_gemm_t<1, 128, OutT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
+  if (cg == 2 && bn == 256) return launch_gemm_t<2, 256, OutT, false, NEXT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
+  if (cg == 2 && bn == 128) return launch_gemm_t<2, 128, OutT, false, NEXT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
+  if (cg == 1 && bn == 256) return launch_gemm_t<1, 256, OutT, false, NEXT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
+  return launch_gemm_t<1, 128, OutT, false, NEXT>(act, wgt, sfa, sfb, la, lu, lu_f16, wc, bias, y, M, N, K, R, tp, stream);
 }
 
 // Split-K plan for a problem with few tiles: 128 x 128 tiles, each tile's slabs shared by S CTAs that
@@ -717,8 +755,10 @@ int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, 
   if (tp.n_peers < 0 || tp.n_peers > 7) return SVDQ_ERR_SHAPE;
   if (tp.y_ld > 0 && (tp.col0 < 0 || tp.col0 % 64 != 0 || tp.col0 + N > tp.y_ld || tp.y_ld % 8 != 0)) return SVDQ_ERR_SHAPE;
   if (tp.y_ld <= 0 && tp.n_peers > 0) return SVDQ_ERR_SHAPE;
+  const bool next = tp.smooth_next != nullptr;
+  if (next && (tp.qout == nullptr || tp.oscales == nullptr || tp.y_ld > 0 || variant >= 10000)) return SVDQ_ERR_UNSUPPORTED;
   int cg, bn;
-  if (variant == 0 || variant >= 10000) {
+  if (!next && (variant == 0 || variant >= 10000)) {
     // split-K: planned (variant 0, plain form, workspace large enough) or forced by the caller
     int s = 1;
     if (variant == 0 && tp.y_ld <= 0 && tp.ws != nullptr) {
@@ -765,9 +805,11 @@ int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, 
   if ((cg != 1 && cg != 2) || (bn != 128 && bn != 256)) return SVDQ_ERR_UNSUPPORTED;
   if (M % (128 * cg) != 0 || N % bn != 0) return SVDQ_ERR_SHAPE;
   if (dtype == SVDQ_DTYPE_F16)
-    return launch_gemm_dt<__half>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, nullptr, wcscales, bias, y, M, N, K, R, tp, stream);
+    return next ? launch_gemm_dt<__half, true>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, nullptr, wcscales, bias, y, M, N, K, R, tp, stream)
+                : launch_gemm_dt<__half, false>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, nullptr, wcscales, bias, y, M, N, K, R, tp, stream);
   if (dtype == SVDQ_DTYPE_BF16)
-    return launch_gemm_dt<__nv_bfloat16>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R, tp, stream);
+    return next ? launch_gemm_dt<__nv_bfloat16, true>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R, tp, stream)
+                : launch_gemm_dt<__nv_bfloat16, false>(cg, bn, act, wgt, ascales_swz, wscales_swz, lora_act16, lora_up, lora_up_f16, wcscales, bias, y, M, N, K, R, tp, stream);
   return SVDQ_ERR_DTYPE;
 }
 

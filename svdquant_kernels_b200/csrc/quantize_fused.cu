@@ -76,7 +76,7 @@ struct Cfg {
   // A multiple of the group count: a group then always meets the same stages, and the slab it waits
   // for is the direct successor (in that stage) of one it consumed itself.  A one-bit phase parity
   // cannot tell "one revolution behind" from "one ahead"; this rule makes the second impossible.
-  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : (STAGES_RAW / QUANT_GROUPS) * QUANT_GROUPS;
+  static constexpr int STAGES = ((STAGES_RAW > 12 ? 12 : STAGES_RAW) / QUANT_GROUPS) * QUANT_GROUPS;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
   static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + 1024;   // ring, barriers, scale-constant table
   static constexpr int TMEM_COLS = RP < 32 ? 32 : RP;             // power of two >= 32

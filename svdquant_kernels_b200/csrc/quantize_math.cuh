@@ -114,7 +114,8 @@ __device__ __forceinline__ uint32_t cvt_e2m1x8(float2 a, float2 b, float2 c, flo
   return r;
 }
 
-// One 16-element group (smoothed, fp32): amax, scale byte, eight code bytes.
+// One 16-element group (smoothed, fp32): amax, scale byte, eight code bytes.  scale_lut: the table
+// fill_scale_lut made in shared memory, or null to work the two constants out on the spot.
 __device__ __forceinline__ void quantize_group(float2 (&f)[8], const float2* scale_lut,
                                                uint32_t& code_lo, uint32_t& code_hi, uint32_t& sbyte) {
   const float m0 = max3abs(f[0].x, f[0].y, f[1].x), m1 = max3abs(f[1].y, f[2].x, f[2].y);
@@ -128,7 +129,7 @@ __device__ __forceinline__ void quantize_group(float2 (&f)[8], const float2* sca
   s = fminf(fmaxf(s, 1e-12f), 448.0f);
   const uint32_t sb = static_cast<uint32_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3));
   sbyte = sb;
-  const float2 k = scale_lut[sb];
+  const float2 k = scale_lut != nullptr ? scale_lut[sb] : scale_constants(sb);
   if (k.x != 0.0f) {
     // m = trunc(4 v / 2^E) keeps the sign of v (also as -0 for a small negative v, whose code is
     // "negative zero" in the reference too; v itself is never -0 here: inputs were made +0 and

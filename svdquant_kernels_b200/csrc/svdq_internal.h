@@ -43,6 +43,12 @@ struct GemmTp {
   // split-K workspace (plain form only): ticket counters (zero between launches), then fp32 partial tiles
   void* ws = nullptr;
   size_t ws_bytes = 0;
+  // next-layer quantisation in the epilogue (plain form only): smooth_next [N] in the output type, qout
+  // [M, N/2], oscales [N/16, M] and optionally the tensor-core twin of oscales
+  const void* smooth_next = nullptr;
+  void* qout = nullptr;
+  void* oscales = nullptr;
+  void* oscales_swz = nullptr;
 };
 constexpr size_t kSplitTicketBytes = 1024;     // 256 ticket counters
 constexpr int kSplitMaxTiles = 74;             // split-K is for problems with at most this many 128 x 128 tiles

@@ -286,11 +286,18 @@ def gemm_w4a4(
     use_2cta: bool = False,                 # accepted for call-site compatibility
     tiler_mn: Optional[Tuple[int, int]] = None,
     lora_schedule: str = "interleave",
+    smooth_next: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
     _columns: Optional[Tuple[torch.Tensor, list, int]] = None,
     _splits: Optional[int] = None,
 ) -> torch.Tensor:
-    """Problems with few output tiles (a few hundred rows) take the split-K form (svdq_gemm_w4a4_ws) with
+    """`smooth_next [N]` (the optional argument of the reference's gemm_w4a4_ref,
+    baseline/kernels/gemm_w4a4/ref.py:80-87): the call returns `(y, qout, oscales)`, where qout
+    `[M, N/2]` / oscales `[N/16, M]` are the NVFP4 codes and scales of the fp32 result (before its
+    cast) divided by smooth_next - the `act` / `ascales` of a following W4A4 linear, made in this
+    GEMM's epilogue instead of by a quantizer pass over y.
+
+    Problems with few output tiles (a few hundred rows) take the split-K form (svdq_gemm_w4a4_ws) with
     a workspace cached per device and stream; `_splits = S` forces S CTAs per 128 x 128 tile, `_splits = 1`
     forbids splitting.
 
@@ -369,6 +376,21 @@ def gemm_w4a4(
         y = out
     else:
         y = torch.empty((M, N), dtype=out_dtype, device=dev)
+    if smooth_next is not None:
+        assert smooth_next.is_cuda and smooth_next.shape == (N,), f"smooth_next must be [N]; got {tuple(smooth_next.shape)}"
+        assert _splits is None or _splits == 1
+        sn = smooth_next.to(out_dtype).contiguous()
+        qout = torch.empty((M, N // 2), dtype=torch.uint8, device=dev)
+        oscales = torch.empty((N // 16, M), dtype=torch.float8_e4m3fn, device=dev)
+        oswz = torch.empty(M * (N // 16), dtype=torch.uint8, device=dev) if N % 64 == 0 else None
+        with _on_device(dev):
+            rc = lib.svdq_gemm_w4a4_next(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc), _ptr(b),
+                                         _ptr(y), _ptr(sn), _ptr(qout), _ptr(oscales), _ptr(oswz), M, N, K, R,
+                                         _DT[out_dtype], variant, _stream(dev))
+        _lib.check(rc, "gemm_w4a4_next")
+        if oswz is not None:
+            _attach(oscales, oswz)
+        return y, qout, oscales
     ws = None
     if _splits is not None and _splits > 1:
         variant = 10000 * _splits + 128

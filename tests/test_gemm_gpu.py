@@ -246,3 +246,104 @@ def test_split_k_is_deterministic():
     torch.cuda.synchronize()
     assert_device_clean()
     assert all(torch.equal(ys[0], y) for y in ys[1:])
+
+
+# ------------------------------------------------------------------------------------------------
+# next-layer quantisation in the epilogue (smooth_next -> qout, oscales; baseline/kernels/gemm_w4a4/ref.py:80-87)
+# ------------------------------------------------------------------------------------------------
+def _next_case(M, K, N, R, dtype, seed, tiler=None, wc=True, bias=True):
+    ops = _ops()
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    x[:, torch.randperm(K, generator=g)[:4]] *= 20
+    x = x.to(dtype)
+    sm = x.float().abs().amax(0).pow(0.5).clamp_min(1e-2).to(dtype)
+    w = torch.randn(N, K, generator=g) * 0.02 / sm.float()[None, :]
+    ld = (torch.randn(K, R, generator=g) / K ** 0.5).to(dtype)
+    lu = (torch.randn(N, R, generator=g) * 0.01).to(dtype)
+    b = (torch.randn(N, generator=g) * 0.01).to(dtype) if bias else None
+    c = (torch.rand(N, generator=g) + 0.5).to(dtype) if wc else None
+    sn = (torch.rand(N, generator=g) * 1.5 + 0.25).to(dtype)
+    dev = "cuda"
+    act, asc, la = ops.quantize_w4a4_act_fuse_lora(x.to(dev), ld.to(dev), sm.to(dev))
+    wgt, wsc = ops.quantize_nvfp4_rows(w.to(dev), pad_size=1)
+    has_lora = R > 0
+    args = (act, wgt, asc, wsc, la if has_lora else None, lu.to(dev) if has_lora else None,
+            None if c is None else c.to(dev), None if b is None else b.to(dev), dtype)
+    y, qout, osc = ops.gemm_w4a4(*args, tiler_mn=tiler, smooth_next=sn.to(dev))
+    y_alone = ops.gemm_w4a4(*args, tiler_mn=tiler)
+    torch.cuda.synchronize()
+    assert_device_clean()
+    assert torch.equal(y, y_alone), "y must not depend on whether the next layer's codes are asked for"
+    _, _, o_q, o_s = O.gemm_w4a4(u8(act), u8(wgt), u8(asc), u8(wsc), la.cpu().numpy() if has_lora else None,
+                                 bits(lu) if has_lora else None, None if c is None else bits(c), None if b is None else bits(b),
+                                 "fp16" if dtype == torch.float16 else "bf16", smooth_next_bits=bits(sn))
+    assert tuple(qout.shape) == o_q.shape and tuple(osc.shape) == o_s.shape
+    twin = ops._attached(osc)
+    if N % 64 == 0:
+        assert twin is not None and (twin.cpu().numpy() == O.swizzle_scales(u8(osc))).all(), "tensor-core twin of oscales differs"
+    return u8(qout), u8(osc), o_q, o_s
+
+
+@pytest.mark.parametrize("tiler", [None, (128, 128), (128, 256), (256, 128), (256, 256)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_next_layer_codes_are_bit_exact_where_y_is_exact(dtype, tiler):
+    """No LoRA and K = 256: every y is a sum of fp4 x fp4 x e4m3 x e4m3 products that fp32 adds without
+    rounding in any order, so the kernel's fp32 y equals the oracle's and the next layer's codes and
+    scales must match bit for bit (wcscales and bias are applied with the same two roundings)."""
+    q, s, o_q, o_s = _next_case(256, 256, 256, 0, dtype, seed=41, tiler=tiler)
+    assert (s == o_s).all(), "scale bytes differ"
+    assert (q == o_q).all(), "code bytes differ"
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N,R", [(256, 1024, 512, 64), (512, 3840, 1280, 128), (384, 640, 384, 16)])
+def test_next_layer_codes_with_lora(M, K, N, R, dtype):
+    """With LoRA and a long K the kernel's fp32 y differs from the oracle's in its last bits (summation
+    order, 16-bit lora_act), so a value that sits on a rounding bound may fall on the other side: at
+    least 99.9 % of codes and scales equal; where the scale byte agrees, a differing code is the
+    neighbouring one (one step of the 4-bit grid, which is why a relative L2 norm of the
+    dequantised tensors says little here: one flipped code in a thousand already moves it by 1e-2)."""
+    q, s, o_q, o_s = _next_case(M, K, N, R, dtype, seed=43 + M)
+    assert (s != o_s).mean() <= 1e-3
+    c, o_c = O.unpack_nibbles(q), O.unpack_nibbles(o_q)
+    assert (c != o_c).mean() <= 1e-3
+    same_scale = np.repeat((s == o_s).T, 16, axis=1)                   # [M, N]: the group's scale byte agrees
+    differ = (c != o_c) & same_scale
+    mag, o_mag = (c & 7).astype(np.int32), (o_c & 7).astype(np.int32)
+    assert (np.abs(mag - o_mag)[differ] <= 1).all(), "a differing code is not a neighbour"
+    assert O.rel_l2(O.dequantize_nvfp4_rows(q, s), O.dequantize_nvfp4_rows(o_q, o_s)) <= 2e-2
+
+
+def test_next_layer_fixture_and_chained_linears():
+    """The reference-made fixture through the kernel, then two linears back to back: the second GEMM
+    consumes the first one's (qout, oscales) directly and must equal the GEMM run on a separate
+    quantisation of the same fp32 values (same codes -> same result, bit for bit)."""
+    from conftest import load_golden, next_golden_names
+    ops = _ops()
+    for name in next_golden_names():
+        g = load_golden(name)
+        dt = NAME_DT[g["dtype"]]
+        M_pad, N = g["act"].shape[0], g["wgt"].shape[0]
+        act = torch.from_numpy(g["act"]).cuda()
+        wgt = torch.from_numpy(g["wgt"]).cuda()
+        asc = torch.from_numpy(g["ascales"]).cuda().view(torch.float8_e4m3fn)
+        wsc = torch.from_numpy(g["wscales"]).cuda().view(torch.float8_e4m3fn)
+        la = torch.from_numpy(g["lora_act"]).cuda()
+        y, qout, osc = ops.gemm_w4a4(act, wgt, asc, wsc, la, from_bits(g["lora_up"], dt), from_bits(g["wcscales"], dt),
+                                     from_bits(g["bias"], dt), dt, smooth_next=from_bits(g["smooth_next"], dt))
+        torch.cuda.synchronize()
+        if g["exact"]:
+            assert (u8(qout) == g["qout"]).all() and (u8(osc) == g["oscales"]).all(), name
+        else:
+            assert (u8(osc) != g["oscales"]).mean() <= 1e-3 and \
+                (O.unpack_nibbles(u8(qout)) != O.unpack_nibbles(g["qout"])).mean() <= 1e-3, name
+        # chained: qout / oscales of layer 1 are the activations of a second linear with K2 = N
+        gen = torch.Generator().manual_seed(5)
+        w2 = (torch.randn(256, N, generator=gen) * 0.02).cuda()
+        wgt2, wsc2 = ops.quantize_nvfp4_rows(w2, pad_size=1)
+        y2 = ops.gemm_w4a4(qout, wgt2, osc, wsc2, None, None, None, None, dt)
+        y2_ref_bits, _ = oracle_gemm(u8(qout), u8(wgt2), u8(osc), u8(wsc2), None, None, None, None, dt)
+        torch.cuda.synchronize()
+        assert rel_l2_vs_bits(y2, y2_ref_bits) <= TOL, name
+    assert_device_clean()
