@@ -47,6 +47,12 @@ enum {
   SVDQ_QUANT_FORCE_STREAM = 0x100000
 };
 
+/* bits that may be OR-ed into the `variant` argument of the GEMM entry points */
+enum {
+  SVDQ_GEMM_LORA_INTERLEAVE = 1 << 24,  /* a tile's LoRA-up slabs spread evenly among its main K slabs */
+  SVDQ_GEMM_LORA_AT_END = 1 << 25       /* ... after them */
+};
+
 const char* svdq_status_string(int status);
 int svdq_version(void);
 
@@ -168,6 +174,11 @@ int svdq_lora_up_to_f16(const void* lora_up_bf16_host, void* out_f16_host, long 
  * Contract: M % 128 == 0, N % 128 == 0, K % 64 == 0, R % 16 == 0 (svdq_gemm_w4a4_supported).
  * variant: 0 = let the library pick; 128 / 256 = one CTA per 128 x variant tile;
  *          2128 / 2256 = CTA pairs on 256 x 128 / 256 x 256 tiles (needs M % 256 == 0).
+ *          OR-ed with SVDQ_GEMM_LORA_INTERLEAVE or SVDQ_GEMM_LORA_AT_END it also fixes where a tile's
+ *          LoRA-up slabs run: spread evenly among its main K slabs (launch_v2's lora_schedule =
+ *          "interleave", cute_kernels/gemm_w4a4/kernel_v2_fa4.py:126, :299-303) or after them; with
+ *          neither bit the library takes the one it measured faster.  The result is the same sum in a
+ *          different order (within the GEMM tolerance of each other, not bit-identical).
  *   y = cast( (deq(act) deq(wgt)^T + lora_act16 lora_up^T) * wcscales + bias )
  */
 int svdq_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,

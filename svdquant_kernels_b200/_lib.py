@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_PKG_DIR, "libsvdq_b200.so")
 DTYPE_F16, DTYPE_BF16, DTYPE_F32 = 0, 1, 2
 QUANT_AUTO, QUANT_FORCE_GENERIC, QUANT_FORCE_FUSED, QUANT_FORCE_STREAM = 0, 1, 2, 0x100000
 OK = 0
+GEMM_LORA_INTERLEAVE, GEMM_LORA_AT_END = 1 << 24, 1 << 25
 
 # name -> (restype, argtypes); kept in the order of include/svdq_b200.h
 SIGNATURES = {

@@ -132,6 +132,8 @@ struct Params {
   // ws_tickets[tile], and the CTA that draws the last ticket adds the partials in split order, runs
   // the epilogue and puts the ticket counter back to zero.
   int splits;
+  int interleave;       // 1: LoRA slabs spread evenly among the main slabs of a tile; 0: after them
+  int stride1, stride2; // interleaved: positions between LoRA slabs of a tile with one / two LoRA passes
   float4* ws_partials;
   unsigned int* ws_tickets;
   // Next-layer quantisation (NEXT kernels only): the fp32 result, before its cast, divided by
@@ -260,7 +262,29 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   auto slab_range = [&](int split, int kt_all, int& lo, int& hi) {
     if (SK) { lo = split * kt_all / S; hi = (split + 1) * kt_all / S; } else { lo = 0; hi = kt_all; }
   };
-
+  // Which slab runs at position pos of a tile's kt_all = kt_main + n_lora slabs.  Slab numbers below
+  // kt_main are main slabs, the others LoRA slabs.  End-grouped: position = number.  Interleaved (the
+  // reference's schedule, cute_kernels/gemm_w4a4/kernel_v2_fa4.py:299-303): LoRA slab j sits at position
+  // (j + 1) * stride - 1 with stride = kt_all / n_lora, the main slabs fill the rest in order.  Every
+  // role walks the positions with one of these and the same arguments, so all agree.  No division in
+  // the per-slab step: the issuing threads have a few hundred cycles per slab for everything.
+  struct SlabWalk {
+    int kt_main, n_lora, stride, lora_done, next_lora;
+    __device__ __forceinline__ void start(int kt_main_, int kt_all, int interleave, int stride_, int first_pos) {
+      kt_main = kt_main_;
+      n_lora = interleave ? kt_all - kt_main_ : 0;
+      stride = stride_;
+      lora_done = 0;
+      if (n_lora > 0 && first_pos > 0) { lora_done = first_pos / stride; if (lora_done > n_lora) lora_done = n_lora; }
+      next_lora = (lora_done + 1) * stride - 1;
+    }
+    __device__ __forceinline__ int at(int pos) {
+      if (lora_done < n_lora && pos == next_lora) { const int kt = kt_main + lora_done; ++lora_done; next_lora += stride; return kt; }
+      return pos - lora_done;
+    }
+  };
+  // stride of a tile with one / two LoRA passes (worked out on the host)
+  auto lora_stride = [&](bool fp16_pass) -> int { return (kBf16 && !fp16_pass) ? p.stride2 : p.stride1; };
   if (warp == EPI_WARPS) {
     // ------------------------------ producer (both CTAs) ------------------------------
     uint32_t it = 0;
@@ -275,7 +299,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int kt_all = kt_main + lora_parts(la_fp16) * lora_slabs;
       int kt_lo, kt_hi;
       slab_range(split, kt_all, kt_lo, kt_hi);
-      for (int kt = kt_lo; kt < kt_hi; ++kt, ++it) {
+      SlabWalk walk;
+      walk.start(kt_main, kt_all, p.interleave, lora_stride(la_fp16), kt_lo);
+      for (int pos = kt_lo; pos < kt_hi; ++pos, ++it) {
+        const int kt = walk.at(pos);
         const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
         if (!uwait(&empty[s], ph ^ 1, ctx, kDevWaitEmpty, it)) { ok = false; break; }
         uint8_t* st = smem + s * C::STAGE_BYTES;
@@ -339,7 +366,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t idesc_lora = la_fp16 ? kIdescLoraF16 : kIdescLora;
         int kt_lo, kt_hi;
         slab_range(split, kt_all, kt_lo, kt_hi);
-        for (int kt = kt_lo; kt < kt_hi; ++kt, ++it) {
+        SlabWalk walk;
+        walk.start(kt_main, kt_all, p.interleave, lora_stride(la_fp16), kt_lo);
+        for (int pos = kt_lo; pos < kt_hi; ++pos, ++it) {
+          const int kt = walk.at(pos);
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
           if (!uwait(&full[s], ph, ctx, kDevWaitFull, it)) { ok = false; break; }
           const bool main_slab = kt < kt_main;
@@ -358,17 +388,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int j = 0; j < 4; ++j)
                 if (j < nkb)
                   mma_nvfp4<CG>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
-                                kIdescMain, tsfa + j * 4, tsfb + j * (BN / 32), ((kt - kt_lo) | j) != 0 ? 1u : 0u);
+                                kIdescMain, tsfa + j * 4, tsfb + j * (BN / 32), ((pos - kt_lo) | j) != 0 ? 1u : 0u);
               tc_commit_local<CG>(&sf_empty[sb]);   // scale buffer reusable once these MMAs are done
             } else {
 #pragma unroll
               for (int j = 0; j < 4; ++j)
                 if (j < nkb)
                   mma_f16<CG>(tmem_acc, smem_desc(kDescAB, a_addr + j * 32), smem_desc(kDescAB, b_addr + j * 32),
-                              idesc_lora, ((kt - kt_lo) | j) != 0 ? 1u : 0u);
+                              idesc_lora, ((pos - kt_lo) | j) != 0 ? 1u : 0u);
             }
             tc_commit_mask<CG>(&empty[s], kMask);          // stage reusable (in both CTAs) once these MMAs have read it
-            if (kt == kt_hi - 1) tc_commit_mask<CG>(&acc_full[as], kMask);    // accumulator complete
+            if (pos == kt_hi - 1) tc_commit_mask<CG>(&acc_full[as], kMask);    // accumulator complete
           }
           __syncwarp();
           if (main_slab) ++sf_it;
@@ -385,10 +415,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       bool ok = true;
       for (int w = pair; w < total_work && ok; w += num_pairs) {
         const int tile = SK ? w / S : w, split = SK ? w - tile * S : 0;
-        const int kt_all = kt_main + lora_parts(lora_fp16(tile % p.tiles_m)) * lora_slabs;
+        const bool la_fp16 = lora_fp16(tile % p.tiles_m);
+        const int kt_all = kt_main + lora_parts(la_fp16) * lora_slabs;
         int kt_lo, kt_hi;
         slab_range(split, kt_all, kt_lo, kt_hi);
-        for (int kt = kt_lo; kt < kt_hi; ++kt, ++it) {
+        SlabWalk walk;
+        walk.start(kt_main, kt_all, p.interleave, lora_stride(la_fp16), kt_lo);
+        for (int pos = kt_lo; pos < kt_hi; ++pos, ++it) {
+          const int kt = walk.at(pos);
           // Every slab's barrier is waited on in order, LoRA slabs (which carry no scales) included: a
           // waiter that skipped ahead could get two ring revolutions in front of the producer, where the
           // parity of a barrier no longer tells the revolutions apart.
@@ -676,6 +710,12 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   p.col0 = tp.y_ld > 0 ? tp.col0 : 0; p.y_ld = y_ld; p.n_peers = tp.n_peers;
   for (int d = 0; d < 7; ++d) p.y_peer[d] = d < tp.n_peers ? tp.y_peer[d] : nullptr;
   p.splits = SK ? splits : 1;
+  p.interleave = tp.interleave;
+  {
+    const int kt_main = (K + gemm::BK - 1) / gemm::BK, ls = (R + 63) / 64;
+    p.stride1 = ls > 0 ? (kt_main + ls) / ls : 1;
+    p.stride2 = ls > 0 ? (kt_main + 2 * ls) / (2 * ls) : 1;
+  }
   p.ws_tickets = static_cast<unsigned int*>(tp.ws);
   p.ws_partials = tp.ws != nullptr ? reinterpret_cast<float4*>(static_cast<uint8_t*>(tp.ws) + kSplitTicketBytes) : nullptr;
   p.smooth_next = tp.smooth_next;
@@ -745,13 +785,24 @@ size_t gemm_split_workspace_bytes(int M, int N, int K, int R) {
   return kSplitTicketBytes + static_cast<size_t>(M / 128) * (N / 128) * s * (128 * 128 * 4);
 }
 
+// Default LoRA schedule: after the main slabs.  Same-box A/B on the four benchmark shapes: interleaved
+// 27.1 / 121.0 / 102.4 / 55.0 us against 27.4 / 120.5 / 102.6 / 55.0 us at the end (within run-to-run noise; the
+// reference measured +0.5 % for its interleave, docs/gotchas/cute_dsl.md:368-377).
+constexpr int kLoraInterleaveDefault = 0;
+
 // variant: 0 = choose; 128 / 256 = one CTA per tile with that N tile; 2128 / 2256 = CTA pairs (256-row tiles);
 // 10000 * S + 128 = split-K with S CTAs per 128 x 128 tile (needs the workspace)
 int launch_gemm_w4a4(const void* act, const void* wgt, const void* ascales_swz, const void* wscales_swz,
                      const void* lora_act16, const void* lora_up, const void* lora_up_f16, const void* wcscales,
                      const void* bias, void* y, int M, int N, int K, int R, int dtype, int variant,
-                     const GemmTp& tp, cudaStream_t stream) {
+                     const GemmTp& tp_in, cudaStream_t stream) {
   if (!gemm_supported(M, N, K, R)) return SVDQ_ERR_SHAPE;
+  // LoRA schedule bits of `variant`: interleaved, end-grouped, or (neither) the library's default
+  GemmTp tp = tp_in;
+  if (variant & SVDQ_GEMM_LORA_INTERLEAVE) tp.interleave = 1;
+  else if (variant & SVDQ_GEMM_LORA_AT_END) tp.interleave = 0;
+  else tp.interleave = kLoraInterleaveDefault;
+  variant &= ~(SVDQ_GEMM_LORA_INTERLEAVE | SVDQ_GEMM_LORA_AT_END);
   if (tp.n_peers < 0 || tp.n_peers > 7) return SVDQ_ERR_SHAPE;
   if (tp.y_ld > 0 && (tp.col0 < 0 || tp.col0 % 64 != 0 || tp.col0 + N > tp.y_ld || tp.y_ld % 8 != 0)) return SVDQ_ERR_SHAPE;
   if (tp.y_ld <= 0 && tp.n_peers > 0) return SVDQ_ERR_SHAPE;

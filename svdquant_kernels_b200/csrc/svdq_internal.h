@@ -43,6 +43,7 @@ struct GemmTp {
   // split-K workspace (plain form only): ticket counters (zero between launches), then fp32 partial tiles
   void* ws = nullptr;
   size_t ws_bytes = 0;
+  int interleave = 0;            // LoRA slabs spread among the main slabs (1) or after them (0)
   // next-layer quantisation in the epilogue (plain form only): smooth_next [N] in the output type, qout
   // [M, N/2], oscales [N/16, M] and optionally the tensor-core twin of oscales
   const void* smooth_next = nullptr;

@@ -343,6 +343,11 @@ def gemm_w4a4(
         assert tiler_mn[0] in (128, 256) and tiler_mn[1] in (128, 256)
         assert M % tiler_mn[0] == 0 and N % tiler_mn[1] == 0
         variant = (2000 if tiler_mn[0] == 256 else 0) + tiler_mn[1]
+    # where a tile's LoRA-up slabs run: "interleave" (launch_v2's default spelling) leaves the choice to
+    # the library, "interleaved" / "at_end" fix it
+    assert lora_schedule in ("interleave", "interleaved", "at_end", "end"), f"unknown lora_schedule {lora_schedule!r}"
+    sched = _lib.GEMM_LORA_INTERLEAVE if lora_schedule == "interleaved" else \
+        (_lib.GEMM_LORA_AT_END if lora_schedule in ("at_end", "end") else 0)
 
     lib = _lib.load()
     dev = act.device
@@ -368,7 +373,7 @@ def gemm_w4a4(
         with _on_device(dev):
             rc = lib.svdq_gemm_w4a4_columns(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc),
                                             _ptr(b), _ptr(y_full), arr, len(peer_ptrs), n_total, col0, M, N, K, R,
-                                            _DT[out_dtype], variant, _stream(dev))
+                                            _DT[out_dtype], variant | sched, _stream(dev))
         _lib.check(rc, "gemm_w4a4_columns")
         return y_full
     if out is not None:
@@ -386,7 +391,7 @@ def gemm_w4a4(
         with _on_device(dev):
             rc = lib.svdq_gemm_w4a4_next(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc), _ptr(b),
                                          _ptr(y), _ptr(sn), _ptr(qout), _ptr(oscales), _ptr(oswz), M, N, K, R,
-                                         _DT[out_dtype], variant, _stream(dev))
+                                         _DT[out_dtype], variant | sched, _stream(dev))
         _lib.check(rc, "gemm_w4a4_next")
         if oswz is not None:
             _attach(oscales, oswz)
@@ -402,10 +407,10 @@ def gemm_w4a4(
     with _on_device(dev):
         if ws is not None:
             rc = lib.svdq_gemm_w4a4_ws(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc), _ptr(b),
-                                       _ptr(y), M, N, K, R, _DT[out_dtype], variant, _ptr(ws), ws.numel(), _stream(dev))
+                                       _ptr(y), M, N, K, R, _DT[out_dtype], variant | sched, _ptr(ws), ws.numel(), _stream(dev))
         else:
             rc = lib.svdq_gemm_w4a4(_ptr(a), _ptr(w), _ptr(sa), _ptr(sw), _ptr(la), _ptr(lu), _ptr(lu16), _ptr(wc), _ptr(b),
-                                    _ptr(y), M, N, K, R, _DT[out_dtype], variant, _stream(dev))
+                                    _ptr(y), M, N, K, R, _DT[out_dtype], variant | sched, _stream(dev))
     _lib.check(rc, "gemm_w4a4")
     return y
 

@@ -347,3 +347,33 @@ def test_next_layer_fixture_and_chained_linears():
         torch.cuda.synchronize()
         assert rel_l2_vs_bits(y2, y2_ref_bits) <= TOL, name
     assert_device_clean()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,K,N,R,tiler,splits", [(256, 2560, 512, 128, None, None), (512, 1280, 256, 64, (128, 128), None),
+                                                  (256, 320, 256, 256, (256, 256), None), (128, 2560, 512, 32, None, 3),
+                                                  (256, 64, 128, 16, (128, 128), None)])
+def test_lora_schedules_agree(M, K, N, R, tiler, splits, dtype):
+    """A tile's LoRA-up slabs spread among its main K slabs (the reference's lora_schedule =
+    "interleave", cute_kernels/gemm_w4a4/kernel_v2_fa4.py:299-303) or after them: the same sum in two
+    orders, both within the tolerance of the oracle, for every tile shape, more LoRA slabs than main
+    slabs (K = 64, R = 16 / K = 320, R = 256 in two bf16 passes) and the split-K form."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(17 + M + K)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    w = torch.randn(N, K, generator=g) * 0.02
+    ld = (torch.randn(K, R, generator=g) / K ** 0.5).to(dtype)
+    lu = (torch.randn(N, R, generator=g) * 0.05).to(dtype)
+    dev = "cuda"
+    act, asc, la = ops.quantize_w4a4_act_fuse_lora(x.to(dev), ld.to(dev), None)
+    wgt, wsc = ops.quantize_nvfp4_rows(w.to(dev), pad_size=1)
+    ys = {}
+    for sched in ("interleaved", "at_end", "interleave"):
+        ys[sched] = ops.gemm_w4a4(act, wgt, asc, wsc, la, lu.to(dev), None, None, dtype, tiler_mn=tiler, lora_schedule=sched,
+                                  _splits=splits)
+    torch.cuda.synchronize()
+    assert_device_clean()
+    y_bits, _ = oracle_gemm(u8(act), u8(wgt), u8(asc), u8(wsc), la.cpu().numpy(), lu, None, None, dtype)
+    for sched, y in ys.items():
+        assert rel_l2_vs_bits(y, y_bits) <= TOL, sched
+    assert torch.equal(ys["interleave"], ys["interleaved"]) or torch.equal(ys["interleave"], ys["at_end"])
