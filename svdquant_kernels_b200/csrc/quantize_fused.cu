@@ -63,7 +63,8 @@ constexpr int X_BYTES = TILE_M * 128;      // 8 KB
 #endif
 constexpr int QUANT_GROUPS = SVDQ_QUANT_GROUPS;   // groups of 4 warps take slabs round-robin
 constexpr int QUANT_WARPS = 4 * QUANT_GROUPS;
-constexpr int NUM_THREADS = (2 + QUANT_WARPS) * 32;
+constexpr int AUX_WARPS = 4;                // producer, MMA issuer, two helpers; with two K ranks they exchange the LoRA sums
+constexpr int NUM_THREADS = (AUX_WARPS + QUANT_WARPS) * 32;
 constexpr int TB_BYTES = SLAB_K * 8;       // {smooth, 1/smooth} of a slab's columns
 constexpr int TB_GROUP_STRIDE = 144;       // spacing of the four 128-byte group pieces in a stage
 
@@ -72,13 +73,14 @@ template <int RP>
 struct Cfg {
   static constexpr int W_BYTES = SLAB_K * RP * 2;                 // lora_down slab
   static constexpr int STAGE_BYTES = X_BYTES + W_BYTES + 1024;   // table slab + padding to the 1 KB the swizzled tiles need
-  static constexpr int STAGES_RAW = (232448 - 1024 - 512 - 1024) / STAGE_BYTES;
+  static constexpr int RECV_BYTES = (TILE_M / 2) * RP * 4;        // two K ranks: the peer's partial sums of this CTA's 32 rows
+  static constexpr int STAGES_RAW = (232448 - 1024 - 512 - 1024 - RECV_BYTES) / STAGE_BYTES;
   // A multiple of the group count: a group then always meets the same stages, and the slab it waits
   // for is the direct successor (in that stage) of one it consumed itself.  A one-bit phase parity
   // cannot tell "one revolution behind" from "one ahead"; this rule makes the second impossible.
   static constexpr int STAGES = ((STAGES_RAW > 12 ? 12 : STAGES_RAW) / QUANT_GROUPS) * QUANT_GROUPS;
   static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + 1024;   // ring, barriers, scale-constant table
+  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + 1024 + RECV_BYTES;   // ring, barriers, scale-constant table, receive buffer
   static constexpr int TMEM_COLS = RP < 32 ? 32 : RP;             // power of two >= 32
   static constexpr int EPI_COLS = RP / 4 < 32 ? 32 : RP / 4;      // accumulator columns per epilogue warp
   static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the ring");
@@ -119,10 +121,12 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   uint64_t* full = bars;                       // [STAGES]  producer -> consumers
   uint64_t* empty = bars + C::STAGES;          // [STAGES]  consumers -> producer
   uint64_t* acc_done = bars + 2 * C::STAGES;   // MMA -> epilogue
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  uint64_t* recv_bar = acc_done + 1;           // two K ranks: the peer's partial sums have landed in `recv`
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(recv_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* lora_unfit = tmem_slot + 2;        // bf16 form: some LoRA value this CTA wrote does not fit fp16
   float2* scale_lut = reinterpret_cast<float2*>(smem + C::RING_BYTES + 512);   // per scale byte: {2^(2-E), ~1/(4J)}
+  float4* recv = reinterpret_cast<float4*>(smem + C::RING_BYTES + 512 + 1024);  // [32 rows][RP / 4], slots as partial_slot
   const WaitCtx ctx{abort_flag};
 
   // warp index through a shuffle: provably warp-uniform, so the role branches are convergent code
@@ -148,6 +152,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     *lora_unfit = 0u;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1 + QUANT_WARPS / QUANT_GROUPS); }
     mbar_init(acc_done, 1);
+    mbar_init(recv_bar, 2);                    // the peer's two warps that hold this CTA's rows
     fence_barrier_init();
     tma_prefetch_desc(&tmX);
     if (has_lora) tma_prefetch_desc(&tmW);
@@ -159,6 +164,10 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   qmath::fill_scale_lut(scale_lut, threadIdx.x, NUM_THREADS);
   tc_fence_before_sync();
   __syncthreads();
+  // Two K ranks hand their partial sums to each other with plain remote stores and a remote barrier
+  // arrival, so the partner's barrier must exist before either touches it.  (The CTAs of a cluster
+  // start together; this costs a fraction of a microsecond, before the wait for the kernel ahead.)
+  if (ks == 2 && has_lora) cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_acc = *tmem_slot;
   // set-up done; what follows reads and writes global memory
@@ -216,13 +225,13 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       }
       __syncwarp();
     }
-  } else {
+  } else if (warp >= AUX_WARPS) {
     // ------------------------------ quantize warps ------------------------------
     // Group grp takes slabs grp, grp + QUANT_GROUPS, ...; its warp wq owns rows 16 wq .. 16 wq + 15 of the
     // tile.  Lane l works on 16-column group l % 4 of rows l / 4 and l / 4 + 8 of those, so the four
     // lanes of a quad hold one row's whole 64-column stretch of the slab: their 8-byte code stores
     // fill one 32-byte sector, and their scale bytes are adjacent in the atom layout.
-    const int qw = warp - 2;
+    const int qw = warp - AUX_WARPS;
     const int grp = qw >> 2;
     const int wq = qw & 3;
     const int g = lane & 3;                   // 16-column group inside the slab
@@ -282,11 +291,72 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   // ------------------------------ LoRA epilogue ------------------------------
   // The 64 accumulator rows live in lanes 0-15 of each 32-lane quarter of tensor memory:
   // row r is lane (r % 16) + 32 * (r / 16).
-  if (has_lora) {
+  if (has_lora && ks == 2) {
+    // Two K ranks (the form for tall activations): CTA k owns rows [32 k, 32 k + 32) of the tile.  The four
+    // auxiliary warps do the whole exchange while the quantize warps are still busy with the last slabs:
+    // warp w reads rows 16 w .. 16 w + 15 of the accumulator (lanes 0-15 of its quarter of tensor
+    // memory); rows of the partner go straight into the partner's receive buffer (remote shared-memory
+    // stores, then one remote barrier arrival per warp), own rows wait for the partner's two arrivals,
+    // add the two partial sums (two terms: the order does not matter) and leave for global memory.
+    if (warp < AUX_WARPS) {
+      constexpr uint32_t RP4 = RP / 4;
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_done, 0, ctx, kDevWaitAcc, 0)) != 0;
+      tc_fence_after_sync();
+      const bool mine = static_cast<uint32_t>(warp >> 1) == krank;
+      const uint32_t row_local = 16u * (warp & 1) + (lane & 15);     // row within the owner's 32
+      const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
+      if (!mine) {
+        const uint32_t peer_recv = map_to_cta(smem_u32(recv), krank ^ 1u);
+#pragma unroll 1
+        for (int c0 = 0; c0 < RP; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c0, v);
+          tmem_ld_wait();
+          if (lane < 16) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              st_cluster_f4(peer_recv + partial_slot(row_local, (c0 >> 2) + j, RP4) * 16u,
+                            make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
+          }
+        }
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive_cluster(recv_bar, krank ^ 1u);    // release at cluster scope: the stores above are visible first
+      } else {
+        const bool got = __all_sync(0xffffffffu, mbar_wait_cluster(recv_bar, 0, ctx, kDevWaitMisc, 0x40000)) != 0;
+        const size_t gm = static_cast<size_t>(m0) + 32u * krank + row_local;
+#pragma unroll 1
+        for (int c0 = 0; c0 < RP; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c0, v);
+          tmem_ld_wait();
+          if (lane < 16 && ok && got) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int c = c0 + 4 * j;
+              if (c < p.R) {
+                const float4 t = recv[partial_slot(row_local, (c0 >> 2) + j, RP4)];
+                const float4 o = make_float4(__uint_as_float(v[4 * j]) + t.x, __uint_as_float(v[4 * j + 1]) + t.y,
+                                             __uint_as_float(v[4 * j + 2]) + t.z, __uint_as_float(v[4 * j + 3]) + t.w);
+                *reinterpret_cast<float4*>(p.lora + gm * p.R + c) = o;
+                if (p.lora16 != nullptr) {
+                  store_lora16x4<T>(p.lora16, gm * p.R + c, static_cast<size_t>(p.M_pad) * p.R, o);
+                  if (kBf16 && !fits_f16(o)) atomicOr(lora_unfit, 1u);
+                }
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      asm volatile("bar.sync 3, %0;" ::"n"(AUX_WARPS * 32) : "memory");
+      if (kBf16 && p.lora16 != nullptr && threadIdx.x == 0)
+        lora16_flags(p.lora16, static_cast<size_t>(p.M_pad) * p.R)[m0 / 32 + krank] = *lora_unfit;
+    }
+  } else if (has_lora) {
     constexpr uint32_t RP4 = RP / 4;
     float4* partial = reinterpret_cast<float4*>(smem);       // reuses the ring
-    if (warp >= 2) {
-      const int qw = warp - 2;
+    if (warp >= AUX_WARPS) {
+      const int qw = warp - AUX_WARPS;
       const int quarter = warp & 3;                           // TMEM lanes this warp may read
       const int cpart = qw >> 2;                              // column part
       if (cpart * C::EPI_COLS < RP) {
@@ -353,20 +423,28 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         }
       }
       cluster_sync_all();                                     // nobody leaves while its memory is being read
+      if (kBf16 && p.lora16 != nullptr) {
+        // One "does not fit fp16" word per 32 rows, and KS / 2 CTAs wrote rows of the same block: the
+        // first of them gathers the others' verdicts (all final since the barrier above) and stores
+        // the exact word; nobody leaves before that read is over.
+        const uint32_t share = ks / 2;
+        if (threadIdx.x == 0 && krank % share == 0) {
+          uint32_t unfit = 0u;
+          for (uint32_t j = 0; j < share; ++j) unfit |= ld_cluster_u32(map_to_cta(smem_u32(lora_unfit), krank + j));
+          lora16_flags(p.lora16, static_cast<size_t>(p.M_pad) * p.R)[m0 / 32 + krank / share] = unfit;
+        }
+        cluster_sync_all();
+      }
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (kBf16 && has_lora && p.lora16 != nullptr && threadIdx.x == 0) {
-    // one word per 32 rows: this CTA wrote rows [m0, m0 + 64) alone, or its 64 / KS rows of them
+  if (kBf16 && has_lora && p.lora16 != nullptr && threadIdx.x == 0 && ks == 1) {
+    // one word per 32 rows: this CTA wrote rows [m0, m0 + 64) alone
     uint32_t* flags = lora16_flags(p.lora16, static_cast<size_t>(p.M_pad) * p.R);
     const uint32_t unfit = *lora_unfit;
-    if (ks == 1) { flags[m0 / 32] = unfit; flags[m0 / 32 + 1] = unfit; }
-    else if (ks == 2) flags[m0 / 32 + krank] = unfit;
-    // KS > 2: several CTAs wrote rows of the same 32-row block and none knows the others' verdict, so
-    // all of them store the same "no promise" value (the GEMM then takes its two-pass bf16 route)
-    else flags[m0 / 32 + krank / (ks / 2)] = 1u;
+    flags[m0 / 32] = unfit; flags[m0 / 32 + 1] = unfit;
   }
   if (*abort_flag) {
     const unsigned long long t0 = globaltimer_ns();

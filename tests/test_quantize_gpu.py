@@ -59,14 +59,9 @@ def _check(x, ld, sm, force, pad=256):
             flags = flags[0::2] | (flags[1::2] << 16)
             blocks = -(-la.shape[0] // 32)
             unfit = np.array([not (np.abs(la[32 * b:32 * b + 32]) <= 65504.0).all() for b in range(blocks)])
-            if force >= STREAM:
+            if force >= STREAM or force == FUSED:
+                # a zero word promises that the 32 rows fit fp16: exact in both fused forms, for every K split
                 assert ((flags[:blocks] != 0) == unfit).all(), "fits-fp16 words of lora_act differ"
-            elif force == FUSED:
-                # a zero word promises that the 32 rows fit fp16; with few row tiles (more than two CTAs
-                # per tile) the kernel makes no promise, otherwise the words are exact
-                assert not ((flags[:blocks] == 0) & unfit).any(), "a row block that does not fit fp16 is marked as fitting"
-                if (la.shape[0] // 64) * 4 > 148:
-                    assert ((flags[:blocks] != 0) == unfit).all(), "fits-fp16 words of lora_act differ"
             else:
                 assert (flags[:blocks] != 0).all(), "the CUDA-core path must mark every row block"
     return act, ascales, lora
@@ -320,3 +315,21 @@ def test_cluster_capacity_query():
     assert all(v > 0 for v in caps.values()), caps
     assert caps[1] >= caps[2] >= caps[4] >= caps[8]
     assert lib.svdq_quantizer_max_active_clusters(128, 3, _lib.DTYPE_F16) == -1
+
+
+@pytest.mark.parametrize("M,K", [(256, 3840), (1024, 2560), (2304, 1024)])
+def test_fits_fp16_words_are_exact_for_every_split(M, K):
+    """bf16: the word per 32 rows that tells the GEMM whether lora_act fits fp16 there.  Few rows run with
+    four or eight CTAs per row tile, whose verdicts on a shared 32-row block are gathered through
+    distributed shared memory; many rows with two.  Rows 40-49 and the last 20 rows are blown up past
+    65504, everything else fits: exactly those blocks must be marked."""
+    dtype, R = torch.bfloat16, 64
+    g = torch.Generator().manual_seed(77 + M)
+    x = torch.randn(M, K, generator=g)
+    x[40:50] *= 3000.0
+    x[M - 20:] *= 3000.0
+    ld = torch.randn(K, R, generator=g)                      # large on purpose: |lora_act| ~ 3000 * sqrt(K)
+    _, _, la = _check(x.to(dtype).cuda(), ld.to(dtype).cuda(), None, FUSED)
+    blocks = la.abs().reshape(M // 32, -1).amax(1).cpu()
+    big = blocks > 65504
+    assert big[1] and big[-1] and int(big.sum()) == 2, "the test's inputs do not overflow where they should"
