@@ -444,6 +444,22 @@ def run_ours(args):
     rc, words = _lib.device_status()
     if rc != 0:
         raise SystemExit(f"device status after the timed region: {words}")
+    # The long timed region above runs at the board's power cap (the SM clock settles below its maximum).
+    # For comparison with figures measured in short runs: the same per-kernel graphs replayed twice after
+    # the GPU has idled for half a second, i.e. at the clock a single call or a short burst sees.
+    burst = {}
+    for key, g_ in (("quantizer_us", g_q), ("gemm_us", g_g), ("step_us", g_all)):
+        time.sleep(0.5)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = None
+        for _ in range(2):
+            e0.record()
+            g_.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            t_ = e0.elapsed_time(e1) / steps * 1e3
+            best = t_ if best is None else min(best, t_)
+        burst[key] = best
     ms_per_step = r_all["median_ms"] / steps
     q_us = r_q["median_ms"] / steps * 1e3
     g_us = r_g["median_ms"] / steps * 1e3
@@ -545,6 +561,8 @@ def run_ours(args):
         "quantizer_us": q_us, "gemm_us": g_us, "kernel_sum_us": q_us + g_us,
         "pct_of_10pf_nominal": fig["pct_of_10pf_nominal"],
         "quantizer_pct_of_8tbs_nominal": fig["quantizer_pct_of_8tbs_nominal"],
+        "burst_after_idle": dict(burst, note="the same graphs replayed twice after 0.5 s of idle (min): the clock of a short run, "
+                                             "before the power cap lowers it; the headline figures are the sustained ones"),
         "eager_api_us": eager_api_us, "eager_host_issue_us": host_issue_us,
         "eager_api_note": "wall per step of back-to-back Python calls of the two operators (no graphs), outputs reused through out=",
         "ms_per_step_x_sm_mhz": ms_per_step * (clocks.get("sm_mhz") or 0),

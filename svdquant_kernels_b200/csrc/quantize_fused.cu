@@ -278,7 +278,11 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       for (int rr = 0; rr < 2; ++rr) {
         const int row = row_base + 8 * rr;
         uint32_t clo, chi, sb;
+#ifdef SVDQ_NO_LUT
+        quantize_group(f[rr], nullptr, clo, chi, sb);
+#else
         quantize_group(f[rr], scale_lut, clo, chi, sb);
+#endif
         *reinterpret_cast<uint2*>(act_base + static_cast<size_t>(row) * (p.K >> 1) + (k0 >> 1)) = make_uint2(clo, chi);
         p.scales[static_cast<size_t>(gi) * p.M_pad + m0 + row] = static_cast<uint8_t>(sb);
         if (p.scales_swz != nullptr) p.scales_swz[sf_swizzled_offset(m0 + row, gi, groups)] = static_cast<uint8_t>(sb);

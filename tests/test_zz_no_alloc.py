@@ -73,3 +73,36 @@ def test_static_workspace_refuses_what_does_not_fit():
     assert rc == 7, _lib.status_string(rc)
     torch.cuda.synchronize()
     assert_device_clean()
+
+
+def test_static_workspace_calls_allocate_nothing_and_chain_without_host_syncs():
+    """The point of the entry point: once it has been called on a device, further calls take no device
+    memory from anywhere (free memory as the driver reports it does not move), and calls queued back to
+    back on one stream with no host synchronisation in between - each starts its set-up while the one
+    before it is still running - all return the result of the caller-workspace form."""
+    from svdquant_kernels_b200 import ops
+    dtype = torch.float16
+    args = _inputs(256, 10240, 3072, 32, dtype, 24)
+    act, wgt, asc, wsc, la, lu, c, b = args
+    want = ops.gemm_w4a4(act, wgt, asc, wsc, la, lu, c, b, dtype)
+    rc, y = _static_call(args, dtype)                 # first call on this device may look the array's address up
+    torch.cuda.synchronize()
+    assert rc == 0 and torch.equal(y, want)
+    lib = __import__("svdquant_kernels_b200._lib", fromlist=["load"]).load()
+    sa, sw = ops.swizzle_scales(asc), ops.swizzle_scales(wsc)
+    la16 = ops._lora_act_16(la, dtype)
+    M, N, K, R = act.shape[0], wgt.shape[0], act.shape[1] * 2, lu.shape[1]
+    ys = [torch.empty((M, N), dtype=dtype, device=act.device) for _ in range(10)]
+    p, stream = ops._ptr, ops._stream(act.device)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for y_i in ys:                                     # ten calls queued, nothing waited for
+        rc = lib.svdq_gemm_w4a4_static_ws(p(act), p(wgt), p(sa), p(sw), p(la16), p(lu), None, p(c), p(b), p(y_i), M, N, K, R,
+                                          ops._DT[dtype], 0, stream)
+        assert rc == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, "a call of the allocation-free entry point changed the device's free memory"
+    for i, y_i in enumerate(ys):
+        assert torch.equal(y_i, want), f"queued call {i}"
+    assert_device_clean()
