@@ -39,12 +39,13 @@
 // codes per instruction; see quantize_group.
 //
 // Exact arithmetic.  x / smooth must equal the IEEE quotient.  It is computed
-// as q0 = x*r, e = fma(-s, q0, x), q = fma(e, r, q0) with r = RN(1/s) from the
-// table; for operands with at most 11 significant bits this is the correctly
-// rounded quotient (checked exhaustively over mantissas), provided nothing
-// over- or underflows: the table builder raises a flag when a smooth value lies
-// outside [2^-60, 2^60] (2^16 for bf16) and the kernel then divides with __fdiv_rn.  amax / 6
-// uses the same three-step form (checked exhaustively as well).
+// as fma(x, r_hi, RN(x * r_lo)) with r_hi + r_lo = 1/s to 2^-47 from the table
+// (quantize_math.cuh); for operands with at most 11 significant bits this is the
+// correctly rounded quotient (checked exhaustively over mantissas), provided
+// nothing over- or underflows: the table builder raises a flag when a smooth
+// value lies outside [2^-60, 2^60] (2^16 for bf16) and the kernel then divides
+// with __fdiv_rn.  amax / 6 uses a three-step form q0 = a*r, q = fma(fma(-6, q0, a), r, q0)
+// (checked exhaustively as well).
 #include "nvfp4_math.cuh"
 #include "quantize_math.cuh"
 #include "sm100.cuh"
@@ -63,6 +64,10 @@ constexpr int X_BYTES = TILE_M * 128;      // 8 KB
 #endif
 constexpr int QUANT_GROUPS = SVDQ_QUANT_GROUPS;   // groups of 4 warps take slabs round-robin
 constexpr int QUANT_WARPS = 4 * QUANT_GROUPS;
+#ifndef SVDQ_DIRECT_EXCHANGE
+#define SVDQ_DIRECT_EXCHANGE 1
+#endif
+constexpr bool kDirectExchange = SVDQ_DIRECT_EXCHANGE != 0;
 constexpr int AUX_WARPS = 4;                // producer, MMA issuer, two helpers; with two K ranks they exchange the LoRA sums
 constexpr int NUM_THREADS = (AUX_WARPS + QUANT_WARPS) * 32;
 constexpr int TB_BYTES = SLAB_K * 8;       // {smooth, 1/smooth} of a slab's columns
@@ -88,7 +93,7 @@ struct Cfg {
 };
 
 struct Params {
-  const float2* table;    // [K/2] {-s0, -s1, 1/s0, 1/s1} followed by one flag word, or null (no smoothing)
+  const float2* table;    // [K/2] entries of qmath::smooth_table_entry followed by one flag word, or null (no smoothing)
   uint8_t* act;           // [M_pad, K/2]
   uint8_t* scales;        // [K/16, M_pad]
   uint8_t* scales_swz;    // atom order or null
@@ -167,7 +172,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   // Two K ranks hand their partial sums to each other with plain remote stores and a remote barrier
   // arrival, so the partner's barrier must exist before either touches it.  (The CTAs of a cluster
   // start together; this costs a fraction of a microsecond, before the wait for the kernel ahead.)
-  if (ks == 2 && has_lora) cluster_sync_all();
+  if (kDirectExchange && ks == 2 && has_lora) cluster_sync_all();
   tc_fence_after_sync();
   const uint32_t tmem_acc = *tmem_slot;
   // set-up done; what follows reads and writes global memory
@@ -274,18 +279,24 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 
       const int k0 = k_begin + i * SLAB_K + g * 16;
       const int gi = k0 >> 4;
+#if SVDQ_QUANT_PAIR
+      uint32_t clo[2], chi[2], sb[2];
+      qmath::quantize_group_pair(f[0], f[1], scale_lut, clo, chi, sb);
+#endif
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
         const int row = row_base + 8 * rr;
-        uint32_t clo, chi, sb;
-#ifdef SVDQ_NO_LUT
-        quantize_group(f[rr], nullptr, clo, chi, sb);
+#if SVDQ_QUANT_PAIR
+        const uint32_t c_lo = clo[rr], c_hi = chi[rr], s_b = sb[rr];
 #else
-        quantize_group(f[rr], scale_lut, clo, chi, sb);
+        // one group after the other, each stored as soon as it is done: keeping both groups' results in
+        // registers until the end measured 8 % slower
+        uint32_t c_lo, c_hi, s_b;
+        qmath::quantize_group(f[rr], scale_lut, c_lo, c_hi, s_b);
 #endif
-        *reinterpret_cast<uint2*>(act_base + static_cast<size_t>(row) * (p.K >> 1) + (k0 >> 1)) = make_uint2(clo, chi);
-        p.scales[static_cast<size_t>(gi) * p.M_pad + m0 + row] = static_cast<uint8_t>(sb);
-        if (p.scales_swz != nullptr) p.scales_swz[sf_swizzled_offset(m0 + row, gi, groups)] = static_cast<uint8_t>(sb);
+        *reinterpret_cast<uint2*>(act_base + static_cast<size_t>(row) * (p.K >> 1) + (k0 >> 1)) = make_uint2(c_lo, c_hi);
+        p.scales[static_cast<size_t>(gi) * p.M_pad + m0 + row] = static_cast<uint8_t>(s_b);
+        if (p.scales_swz != nullptr) p.scales_swz[sf_swizzled_offset(m0 + row, gi, groups)] = static_cast<uint8_t>(s_b);
       }
     }
     // every quantize warp is done reading the ring before it is reused below
@@ -295,7 +306,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   // ------------------------------ LoRA epilogue ------------------------------
   // The 64 accumulator rows live in lanes 0-15 of each 32-lane quarter of tensor memory:
   // row r is lane (r % 16) + 32 * (r / 16).
-  if (has_lora && ks == 2) {
+  if (kDirectExchange && has_lora && ks == 2) {
     // Two K ranks (the form for tall activations): CTA k owns rows [32 k, 32 k + 32) of the tile.  The four
     // auxiliary warps do the whole exchange while the quantize warps are still busy with the last slabs:
     // warp w reads rows 16 w .. 16 w + 15 of the accumulator (lanes 0-15 of its quarter of tensor
@@ -461,9 +472,10 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   }
 }
 
-// Per column pair {-s0, -s1, 1/s0, 1/s1}, then one flag word: 1 if any smooth value lies outside
-// [2^-60, 2^60] (2^16 for bf16; negative, zero and NaN count as outside), where the three-step divide
-// could over- or underflow or leave a zero with the wrong sign.
+// Per column pair one table entry (qmath::smooth_table_entry), then one flag word: 1 if any smooth value
+// lies outside [2^-60, 2^60] (2^16 for bf16; negative, zero and NaN count as outside), where the two-step
+// divide could over- or underflow or leave a zero with the wrong sign; the entries then hold the smooth
+// values themselves and the kernels divide with __fdiv_rn.
 template <typename T>
 __global__ void smooth_table_kernel(const T* __restrict__ smooth, float2* __restrict__ table, int K) {
   // upper bound: 2^60 for fp16 inputs; 2^16 for bf16 inputs, whose smallest subnormal (2^-133)
@@ -472,14 +484,16 @@ __global__ void smooth_table_kernel(const T* __restrict__ smooth, float2* __rest
   __shared__ int bad;
   if (threadIdx.x == 0) bad = 0;
   __syncthreads();
-  float4* pairs = reinterpret_cast<float4*>(table);
-  for (int i = threadIdx.x; i < K / 2; i += blockDim.x) {
-    const float s0 = to_f32(smooth[2 * i]), s1 = to_f32(smooth[2 * i + 1]);
-    pairs[i] = make_float4(-s0, -s1, __frcp_rn(s0), __frcp_rn(s1));
-    if (!(s0 >= 8.6736174e-19f && s0 <= kMaxSmooth) || !(s1 >= 8.6736174e-19f && s1 <= kMaxSmooth)) bad = 1;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) {
+    const float s = to_f32(smooth[i]);
+    if (!(s >= 8.6736174e-19f && s <= kMaxSmooth)) bad = 1;      // also: negative, zero or NaN
   }
   __syncthreads();
-  if (threadIdx.x == 0) *reinterpret_cast<uint2*>(table + K) = make_uint2(bad ? 1u : 0u, 0u);
+  const bool exact_divide = bad != 0;
+  float4* pairs = reinterpret_cast<float4*>(table);
+  for (int i = threadIdx.x; i < K / 2; i += blockDim.x)
+    pairs[i] = qmath::smooth_table_entry(to_f32(smooth[2 * i]), to_f32(smooth[2 * i + 1]), exact_divide);
+  if (threadIdx.x == 0) *reinterpret_cast<uint2*>(table + K) = make_uint2(exact_divide ? 1u : 0u, 0u);
 }
 
 }  // namespace qf

@@ -7,12 +7,16 @@
 // and a 128-entry table in shared memory for the two constants that depend on the
 // scale byte.
 //
-// Smoothing divide.  x / s must equal the IEEE quotient: q0 = x*r, e = fma(-s, q0, x),
-// q = fma(e, r, q0) with r = RN(1/s) is the correctly rounded quotient for operands of
-// at most 11 significant bits as long as nothing over- or underflows (checked
-// exhaustively over mantissas on the CPU).  The table therefore holds, per column
-// pair, {-s0, -s1, r0, r1}, and a flag word behind it says whether some s lies outside
-// the safe range, in which case the kernels divide with __fdiv_rn.
+// Smoothing divide.  x / s must equal the IEEE quotient.  With r_hi = RU(1/s) (rounded up) and
+// r_lo = RN(1/s - r_hi) <= 0, r_hi + r_lo equals 1/s to 2^-47, and q = fma(x, r_hi, RN(x * r_lo)) is
+// the correctly rounded quotient for operands of at most 11 significant bits: such a quotient is
+// never closer than 2^-36 (relative) to a midpoint between two fp32 numbers, unless it is exactly
+// representable (checked exhaustively over mantissa pairs on the CPU).  Rounding r_hi UP makes r_lo
+// non-positive (-0 when 1/s is exact), which is what turns a -0 input into a +0 quotient:
+// (-0) * r_lo = +0 and (-0) * r_hi + (+0) = +0, as the reference's sign rule needs.  Nothing may
+// over- or underflow: the table builder sets a flag when a smooth value lies outside the safe range,
+// and then stores {s0, s1, -, -} for the kernels to divide with __fdiv_rn.  Per column pair the table
+// holds {r_hi0, r_hi1, r_lo0, r_lo1}.
 //
 // Codes.  The scale byte is J * 2^E (J = 1..15), so m = trunc(4 v / 2^E) is an integer
 // with v's sign and the E2M1 code is the number of n in {1,3,5,7,10,14,20} with
@@ -27,14 +31,16 @@
 
 #include "nvfp4_math.cuh"
 
+#ifndef SVDQ_QUANT_PAIR
+#define SVDQ_QUANT_PAIR 0   // 1: the two groups of a lane share one branch (quantize_group_pair); measured slower
+#endif
+
 namespace svdq {
 namespace qmath {
 
 // Widen a pair of 16-bit values.  CANON adds +0 first, which turns -0 into +0 and changes nothing
 // else (the reference gives a zero the sign bit only when the value tests < 0).  The smoothing
-// divide of the fast path does the same by itself - for s > 0, q0 = x r keeps the zero's sign,
-// e = fma(-s, q0, x) is +0 and q = fma(e, r, q0) = +0 for either zero - so only the other paths
-// ask for it.
+// divide of the fast path does the same by itself (see above), so only the other paths ask for it.
 template <typename T, bool CANON> __device__ __forceinline__ float2 unpack2(uint32_t v);
 template <> __device__ __forceinline__ float2 unpack2<__half, true>(uint32_t v) {
   return __half22float2(__hadd2(*reinterpret_cast<__half2*>(&v), __float2half2_rn(0.0f)));
@@ -58,25 +64,41 @@ __device__ __forceinline__ void unpack_group(const uint4& lo16, const uint4& hi1
   for (int j = 0; j < 8; ++j) f[j] = unpack2<T, CANON>(w[j]);
 }
 
-// Smoothing divide of one 16-element group; tb points at the group's eight
-// {-s0, -s1, r0, r1} table entries in shared memory (the same address in every lane of a quad column).
+// Smoothing divide of one 16-element group; tb points at the group's eight table entries in shared
+// memory (the same address in every lane of a quad column): {r_hi0, r_hi1, r_lo0, r_lo1}, or
+// {s0, s1, -, -} when the launch divides with __fdiv_rn.
 __device__ __forceinline__ void smooth_divide(float2 (&f)[8], const float4* tb, bool use_fdiv) {
   if (!use_fdiv) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float4 t = tb[j];
+#ifdef SVDQ_DIVIDE3
       const float2 ns = make_float2(t.x, t.y), r = make_float2(t.z, t.w);
       const float2 q0 = __fmul2_rn(f[j], r);
       f[j] = __ffma2_rn(__ffma2_rn(ns, q0, f[j]), r, q0);
+#else
+      f[j] = __ffma2_rn(f[j], make_float2(t.x, t.y), __fmul2_rn(f[j], make_float2(t.z, t.w)));
+#endif
     }
   } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float4 t = tb[j];
-      f[j].x = __fadd_rn(__fdiv_rn(f[j].x, -t.x), 0.0f);           // an underflow to -0 counts as +0
-      f[j].y = __fadd_rn(__fdiv_rn(f[j].y, -t.y), 0.0f);
+      f[j].x = __fadd_rn(__fdiv_rn(f[j].x, t.x), 0.0f);           // an underflow to -0 counts as +0
+      f[j].y = __fadd_rn(__fdiv_rn(f[j].y, t.y), 0.0f);
     }
   }
+}
+
+// Table entry of one column pair (see above); `exact_divide` selects the {s0, s1} form.
+__device__ __forceinline__ float4 smooth_table_entry(float s0, float s1, bool exact_divide) {
+  if (exact_divide) return make_float4(s0, s1, 0.0f, 0.0f);
+#ifdef SVDQ_DIVIDE3
+  return make_float4(-s0, -s1, __frcp_rn(s0), __frcp_rn(s1));
+#endif
+  const float h0 = __frcp_ru(s0), h1 = __frcp_ru(s1);
+  const float e0 = fmaf(-s0, h0, 1.0f), e1 = fmaf(-s1, h1, 1.0f);   // exact: 1 - s * r_hi, <= 0
+  return make_float4(h0, h1, e0 == 0.0f ? -0.0f : __fmul_rn(e0, h0), e1 == 0.0f ? -0.0f : __fmul_rn(e1, h1));
 }
 
 // {2^(2-E), RN(1/(4 J)) (1 + 2^-20)} of scale byte sb = J 2^E; {0, 0} for the two bytes that take the compare path
@@ -114,10 +136,8 @@ __device__ __forceinline__ uint32_t cvt_e2m1x8(float2 a, float2 b, float2 c, flo
   return r;
 }
 
-// One 16-element group (smoothed, fp32): amax, scale byte, eight code bytes.  scale_lut: the table
-// fill_scale_lut made in shared memory, or null to work the two constants out on the spot.
-__device__ __forceinline__ void quantize_group(float2 (&f)[8], const float2* scale_lut,
-                                               uint32_t& code_lo, uint32_t& code_hi, uint32_t& sbyte) {
+// amax of a 16-element group -> scale byte: e4m3(clamp(amax / 6, 1e-12, 448)), the divide correctly rounded
+__device__ __forceinline__ uint32_t group_scale_byte(const float2 (&f)[8]) {
   const float m0 = max3abs(f[0].x, f[0].y, f[1].x), m1 = max3abs(f[1].y, f[2].x, f[2].y);
   const float m2 = max3abs(f[3].x, f[3].y, f[4].x), m3 = max3abs(f[4].y, f[5].x, f[5].y);
   const float m4 = max3abs(f[6].x, f[6].y, f[7].x);
@@ -127,35 +147,67 @@ __device__ __forceinline__ void quantize_group(float2 (&f)[8], const float2* sca
   const float s0 = amax * r6;
   float s = fmaf(fmaf(-6.0f, s0, amax), r6, s0);
   s = fminf(fmaxf(s, 1e-12f), 448.0f);
-  const uint32_t sb = static_cast<uint32_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3));
+  return static_cast<uint32_t>(__nv_cvt_float_to_fp8(s, __NV_SATFINITE, __NV_E4M3));
+}
+
+// Main path of the codes: k = {2^(2-E), ~1/(4J)} of the group's scale byte.
+// m = trunc(4 v / 2^E) keeps the sign of v (also as -0 for a small negative v, whose code is
+// "negative zero" in the reference too; v itself is never -0 here: inputs were made +0 and
+// quotients cannot underflow in this path)
+__device__ __forceinline__ void group_codes_fast(const float2 (&f)[8], float2 k, uint32_t& code_lo, uint32_t& code_hi) {
+  const float2 mult = make_float2(k.x, k.x), rj = make_float2(k.y, k.y);
+  float2 w[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float2 t = __fmul2_rn(f[j], mult);
+    w[j] = __fmul2_rn(make_float2(truncf(t.x), truncf(t.y)), rj);
+  }
+  code_lo = cvt_e2m1x8(w[0], w[1], w[2], w[3]);
+  code_hi = cvt_e2m1x8(w[4], w[5], w[6], w[7]);
+}
+
+// Zero scale (everything non-zero saturates) or the 448 clamp (ratios are unbounded): compare path
+__device__ __forceinline__ void group_codes_compare(const float2 (&f)[8], uint32_t sb, uint32_t& code_lo, uint32_t& code_hi) {
+  float sf = e4m3_to_f32(static_cast<uint8_t>(sb));
+  sf = (sf == 0.0f) ? __uint_as_float(4u) : sf;     // 2^-147 * {.25 .. 5}: positive, below any normal number
+  GroupBounds gb;
+  gb.p[0] = sf * 0.25f; gb.p[1] = sf * 0.75f; gb.p[2] = sf * 1.25f; gb.p[3] = sf * 1.75f;
+  gb.p[4] = sf * 2.5f;  gb.p[5] = sf * 3.5f;  gb.p[6] = sf * 5.0f;
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) lo += (e2m1_code(f[j].x, gb) << (8 * j)) + (e2m1_code(f[j].y, gb) << (8 * j + 4));
+#pragma unroll
+  for (int j = 0; j < 4; ++j) hi += (e2m1_code(f[4 + j].x, gb) << (8 * j)) + (e2m1_code(f[4 + j].y, gb) << (8 * j + 4));
+  code_lo = lo; code_hi = hi;
+}
+
+// One 16-element group (smoothed, fp32): amax, scale byte, eight code bytes.  scale_lut: the table
+// fill_scale_lut made in shared memory, or null to work the two constants out on the spot.
+__device__ __forceinline__ void quantize_group(float2 (&f)[8], const float2* scale_lut,
+                                               uint32_t& code_lo, uint32_t& code_hi, uint32_t& sbyte) {
+  const uint32_t sb = group_scale_byte(f);
   sbyte = sb;
   const float2 k = scale_lut != nullptr ? scale_lut[sb] : scale_constants(sb);
-  if (k.x != 0.0f) {
-    // m = trunc(4 v / 2^E) keeps the sign of v (also as -0 for a small negative v, whose code is
-    // "negative zero" in the reference too; v itself is never -0 here: inputs were made +0 and
-    // quotients cannot underflow in this path)
-    const float2 mult = make_float2(k.x, k.x), rj = make_float2(k.y, k.y);
-    float2 w[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const float2 t = __fmul2_rn(f[j], mult);
-      w[j] = __fmul2_rn(make_float2(truncf(t.x), truncf(t.y)), rj);
-    }
-    code_lo = cvt_e2m1x8(w[0], w[1], w[2], w[3]);
-    code_hi = cvt_e2m1x8(w[4], w[5], w[6], w[7]);
+  if (k.x != 0.0f) group_codes_fast(f, k, code_lo, code_hi);
+  else group_codes_compare(f, sb, code_lo, code_hi);
+}
+
+// Two groups at once.  Their scale chains (amax tree, divide by 6, E4M3 conversion, table look-up) are
+// independent and a few dozen cycles long each; done one group after the other, with the branch on
+// the scale byte in between, the second chain cannot start before the first group's codes are
+// finished.  Here both chains run side by side, then one branch takes both groups through the main
+// path (almost always) or sends each through its own.
+__device__ __forceinline__ void quantize_group_pair(float2 (&f0)[8], float2 (&f1)[8], const float2* scale_lut,
+                                                    uint32_t (&code_lo)[2], uint32_t (&code_hi)[2], uint32_t (&sbyte)[2]) {
+  const uint32_t sb0 = group_scale_byte(f0), sb1 = group_scale_byte(f1);
+  sbyte[0] = sb0; sbyte[1] = sb1;
+  const float2 k0 = scale_lut[sb0], k1 = scale_lut[sb1];
+  if (k0.x != 0.0f && k1.x != 0.0f) {
+    group_codes_fast(f0, k0, code_lo[0], code_hi[0]);
+    group_codes_fast(f1, k1, code_lo[1], code_hi[1]);
   } else {
-    // zero scale (everything non-zero saturates) or the 448 clamp (ratios are unbounded): compare path
-    float sf = e4m3_to_f32(static_cast<uint8_t>(sb));
-    sf = (sf == 0.0f) ? __uint_as_float(4u) : sf;     // 2^-147 * {.25 .. 5}: positive, below any normal number
-    GroupBounds gb;
-    gb.p[0] = sf * 0.25f; gb.p[1] = sf * 0.75f; gb.p[2] = sf * 1.25f; gb.p[3] = sf * 1.75f;
-    gb.p[4] = sf * 2.5f;  gb.p[5] = sf * 3.5f;  gb.p[6] = sf * 5.0f;
-    uint32_t lo = 0, hi = 0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) lo += (e2m1_code(f[j].x, gb) << (8 * j)) + (e2m1_code(f[j].y, gb) << (8 * j + 4));
-#pragma unroll
-    for (int j = 0; j < 4; ++j) hi += (e2m1_code(f[4 + j].x, gb) << (8 * j)) + (e2m1_code(f[4 + j].y, gb) << (8 * j + 4));
-    code_lo = lo; code_hi = hi;
+    if (k0.x != 0.0f) group_codes_fast(f0, k0, code_lo[0], code_hi[0]); else group_codes_compare(f0, sb0, code_lo[0], code_hi[0]);
+    if (k1.x != 0.0f) group_codes_fast(f1, k1, code_lo[1], code_hi[1]); else group_codes_compare(f1, sb1, code_lo[1], code_hi[1]);
   }
 }
 

@@ -14,18 +14,39 @@ def _fma(a, b, c):
     return (a.astype(np.float64) * b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)
 
 
-def test_three_step_quotient_equals_ieee_division_for_11_bit_mantissas():
-    """q0 = x*r; q = fma(fma(-s, q0, x), r, q0) with r = RN(1/s) equals RN(x/s) for every pair of
-    11-bit mantissas (fp16 and, a fortiori, bf16 inputs widened to fp32)."""
+def _smooth_table_entry(s):
+    """(r_hi, r_lo) as the table builder makes them: r_hi = RU(1/s), r_lo = RN((1 - s r_hi) r_hi) <= 0,
+    -0 when the reciprocal is exact (qmath::smooth_table_entry)."""
+    r = f32(f32(1.0) / s)
+    if np.float64(r) * np.float64(s) < 1.0:                 # the product is exact in float64: 24 x 11 bits
+        r = np.nextafter(r, f32(np.inf))
+    assert np.float64(r) * np.float64(s) >= 1.0
+    e = 1.0 - np.float64(r) * np.float64(s)                 # exact, <= 0, at most 11 significant bits
+    e32 = f32(e)
+    assert np.float64(e32) == e
+    return r, (f32(np.float64(e32) * np.float64(r)) if e32 != 0 else f32(-0.0))
+
+
+def test_two_step_quotient_equals_ieee_division_for_11_bit_mantissas():
+    """q = fma(x, r_hi, RN(x * r_lo)) equals RN(x/s) for every pair of 11-bit mantissas (fp16 and, a
+    fortiori, bf16 inputs widened to fp32), and either zero comes out as +0.  The fma is evaluated in
+    80-bit extended precision, whose 64-bit significand holds x*r_hi + t exactly."""
+    ld = np.longdouble
+    assert np.finfo(ld).nmant >= 63, "needs x87 extended precision to model the fma exactly"
     x = np.arange(1024, 2048, dtype=np.float32)
-    bad = 0
+    bad = bad_zero = 0
     for ms in range(1024, 2048):
-        s = np.full_like(x, f32(ms))
-        r = (f32(1.0) / s).astype(np.float32)
-        q0 = (x * r).astype(np.float32)
-        q = _fma(_fma(-s, q0, x), r, q0)
+        s = f32(ms)
+        r_hi, r_lo = _smooth_table_entry(s)
+        assert r_lo <= 0 and np.signbit(r_lo)
+        t = (x.astype(np.float64) * np.float64(r_lo)).astype(np.float32)
+        q = (x.astype(ld) * ld(r_hi) + t.astype(ld)).astype(np.float32)
         bad += int((q != (x / s).astype(np.float32)).sum())
-    assert bad == 0
+        for z in (f32(0.0), f32(-0.0)):
+            tz = f32(np.float64(z) * np.float64(r_lo))
+            qz = f32(ld(z) * ld(r_hi) + ld(tz))
+            bad_zero += int(qz != 0 or np.signbit(qz))
+    assert bad == 0 and bad_zero == 0
 
 
 def test_three_step_division_by_six_is_exact_on_sampled_binades():
