@@ -31,9 +31,6 @@
 
 #include "nvfp4_math.cuh"
 
-#ifndef SVDQ_QUANT_PAIR
-#define SVDQ_QUANT_PAIR 0   // 1: the two groups of a lane share one branch (quantize_group_pair); measured slower
-#endif
 
 namespace svdq {
 namespace qmath {
@@ -72,13 +69,7 @@ __device__ __forceinline__ void smooth_divide(float2 (&f)[8], const float4* tb, 
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float4 t = tb[j];
-#ifdef SVDQ_DIVIDE3
-      const float2 ns = make_float2(t.x, t.y), r = make_float2(t.z, t.w);
-      const float2 q0 = __fmul2_rn(f[j], r);
-      f[j] = __ffma2_rn(__ffma2_rn(ns, q0, f[j]), r, q0);
-#else
       f[j] = __ffma2_rn(f[j], make_float2(t.x, t.y), __fmul2_rn(f[j], make_float2(t.z, t.w)));
-#endif
     }
   } else {
 #pragma unroll
@@ -93,9 +84,6 @@ __device__ __forceinline__ void smooth_divide(float2 (&f)[8], const float4* tb, 
 // Table entry of one column pair (see above); `exact_divide` selects the {s0, s1} form.
 __device__ __forceinline__ float4 smooth_table_entry(float s0, float s1, bool exact_divide) {
   if (exact_divide) return make_float4(s0, s1, 0.0f, 0.0f);
-#ifdef SVDQ_DIVIDE3
-  return make_float4(-s0, -s1, __frcp_rn(s0), __frcp_rn(s1));
-#endif
   const float h0 = __frcp_ru(s0), h1 = __frcp_ru(s1);
   const float e0 = fmaf(-s0, h0, 1.0f), e1 = fmaf(-s1, h1, 1.0f);   // exact: 1 - s * r_hi, <= 0
   return make_float4(h0, h1, e0 == 0.0f ? -0.0f : __fmul_rn(e0, h0), e1 == 0.0f ? -0.0f : __fmul_rn(e1, h1));
@@ -190,25 +178,6 @@ __device__ __forceinline__ void quantize_group(float2 (&f)[8], const float2* sca
   const float2 k = scale_lut != nullptr ? scale_lut[sb] : scale_constants(sb);
   if (k.x != 0.0f) group_codes_fast(f, k, code_lo, code_hi);
   else group_codes_compare(f, sb, code_lo, code_hi);
-}
-
-// Two groups at once.  Their scale chains (amax tree, divide by 6, E4M3 conversion, table look-up) are
-// independent and a few dozen cycles long each; done one group after the other, with the branch on
-// the scale byte in between, the second chain cannot start before the first group's codes are
-// finished.  Here both chains run side by side, then one branch takes both groups through the main
-// path (almost always) or sends each through its own.
-__device__ __forceinline__ void quantize_group_pair(float2 (&f0)[8], float2 (&f1)[8], const float2* scale_lut,
-                                                    uint32_t (&code_lo)[2], uint32_t (&code_hi)[2], uint32_t (&sbyte)[2]) {
-  const uint32_t sb0 = group_scale_byte(f0), sb1 = group_scale_byte(f1);
-  sbyte[0] = sb0; sbyte[1] = sb1;
-  const float2 k0 = scale_lut[sb0], k1 = scale_lut[sb1];
-  if (k0.x != 0.0f && k1.x != 0.0f) {
-    group_codes_fast(f0, k0, code_lo[0], code_hi[0]);
-    group_codes_fast(f1, k1, code_lo[1], code_hi[1]);
-  } else {
-    if (k0.x != 0.0f) group_codes_fast(f0, k0, code_lo[0], code_hi[0]); else group_codes_compare(f0, sb0, code_lo[0], code_hi[0]);
-    if (k1.x != 0.0f) group_codes_fast(f1, k1, code_lo[1], code_hi[1]); else group_codes_compare(f1, sb1, code_lo[1], code_hi[1]);
-  }
 }
 
 }  // namespace qmath
