@@ -76,20 +76,30 @@ constexpr int TB_GROUP_STRIDE = 144;       // spacing of the four 128-byte group
 
 template <int RP>
 struct Cfg {
+  // Two rings.  An x stage holds a 64 x 64 tile of x (8 KB) and the slab's 64 table entries; it is read by
+  // the MMA and by one quantize group and released by both.  A lora_down slab (64 x RP, 16 KB at rank
+  // 128) would make that stage three times as large and the ring a third as deep, and the stage would stay
+  // held for the slab's four MMAs; in a ring of its own, which only the MMA reads, a few stages are enough
+  // (the slabs come out of L2) and the x ring gets the rest of the shared memory.
+  static constexpr int X_STAGE_BYTES = X_BYTES + 1024;            // tile + table slab, padded to the 1 KB swizzled tiles need
   static constexpr int W_BYTES = SLAB_K * RP * 2;                 // lora_down slab
-  static constexpr int STAGE_BYTES = X_BYTES + W_BYTES + 1024;   // table slab + padding to the 1 KB the swizzled tiles need
+  static constexpr int W_STAGES = RP > 128 ? 3 : 4;
+  static constexpr int W_RING_BYTES = W_STAGES * W_BYTES;
   static constexpr int RECV_BYTES = (TILE_M / 2) * RP * 4;        // two K ranks: the peer's partial sums of this CTA's 32 rows
-  static constexpr int STAGES_RAW = (232448 - 1024 - 512 - 1024 - RECV_BYTES) / STAGE_BYTES;
+  static constexpr int STAGES_RAW = (232448 - 1024 - 512 - 1024 - RECV_BYTES - W_RING_BYTES) / X_STAGE_BYTES;
   // A multiple of the group count: a group then always meets the same stages, and the slab it waits
   // for is the direct successor (in that stage) of one it consumed itself.  A one-bit phase parity
   // cannot tell "one revolution behind" from "one ahead"; this rule makes the second impossible.
-  static constexpr int STAGES = ((STAGES_RAW > 12 ? 12 : STAGES_RAW) / QUANT_GROUPS) * QUANT_GROUPS;
-  static constexpr int RING_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int SMEM_BYTES = 1024 + RING_BYTES + 512 + 1024 + RECV_BYTES;   // ring, barriers, scale-constant table, receive buffer
+  static constexpr int STAGES = ((STAGES_RAW > 16 ? 16 : STAGES_RAW) / QUANT_GROUPS) * QUANT_GROUPS;
+  static constexpr int RING_BYTES = STAGES * X_STAGE_BYTES;
+  static constexpr int BARS_OFF = RING_BYTES + W_RING_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + BARS_OFF + 512 + 1024 + RECV_BYTES;   // rings, barriers, scale-constant table, receive buffer
   static constexpr int TMEM_COLS = RP < 32 ? 32 : RP;             // power of two >= 32
   static constexpr int EPI_COLS = RP / 4 < 32 ? 32 : RP / 4;      // accumulator columns per epilogue warp
-  static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the ring");
+  static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the x ring");
   static_assert(STAGES >= QUANT_GROUPS && STAGES % QUANT_GROUPS == 0, "ring depth");
+  static_assert((2 * STAGES + 2 * W_STAGES + 2) * 8 + 64 <= 512, "barrier block");
+  static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
 struct Params {
@@ -122,16 +132,19 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   // 1 KB alignment by pointer arithmetic (not an integer round trip) so that the compiler keeps
   // the shared address space and emits shared-memory loads and stores
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::RING_BYTES);
-  uint64_t* full = bars;                       // [STAGES]  producer -> consumers
-  uint64_t* empty = bars + C::STAGES;          // [STAGES]  consumers -> producer
-  uint64_t* acc_done = bars + 2 * C::STAGES;   // MMA -> epilogue
+  uint8_t* wring = smem + C::RING_BYTES;       // lora_down slabs
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::BARS_OFF);
+  uint64_t* full = bars;                       // [STAGES]    x stage filled
+  uint64_t* empty = bars + C::STAGES;          // [STAGES]    x stage consumed (MMA + one quantize group)
+  uint64_t* wfull = bars + 2 * C::STAGES;      // [W_STAGES]  lora_down slab landed
+  uint64_t* wempty = wfull + C::W_STAGES;      // [W_STAGES]  lora_down slab consumed (MMA)
+  uint64_t* acc_done = wempty + C::W_STAGES;   // MMA -> epilogue
   uint64_t* recv_bar = acc_done + 1;           // two K ranks: the peer's partial sums have landed in `recv`
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(recv_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* lora_unfit = tmem_slot + 2;        // bf16 form: some LoRA value this CTA wrote does not fit fp16
-  float2* scale_lut = reinterpret_cast<float2*>(smem + C::RING_BYTES + 512);   // per scale byte: {2^(2-E), ~1/(4J)}
-  float4* recv = reinterpret_cast<float4*>(smem + C::RING_BYTES + 512 + 1024);  // [32 rows][RP / 4], slots as partial_slot
+  float2* scale_lut = reinterpret_cast<float2*>(smem + C::BARS_OFF + 512);   // per scale byte: {2^(2-E), ~1/(4J)}
+  float4* recv = reinterpret_cast<float4*>(smem + C::BARS_OFF + 512 + 1024);  // [32 rows][RP / 4], slots as partial_slot
   const WaitCtx ctx{abort_flag};
 
   // warp index through a shuffle: provably warp-uniform, so the role branches are convergent code
@@ -156,6 +169,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     *abort_flag = 0;
     *lora_unfit = 0u;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1 + QUANT_WARPS / QUANT_GROUPS); }
+    for (int s = 0; s < C::W_STAGES; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wempty[s], 1); }
     mbar_init(acc_done, 1);
     mbar_init(recv_bar, 2);                    // the peer's two warps that hold this CTA's rows
     fence_barrier_init();
@@ -183,41 +197,55 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
-    const uint32_t stage_bytes = X_BYTES + (has_lora ? C::W_BYTES : 0) + (has_table ? TB_BYTES : 0);
+    const uint32_t stage_bytes = X_BYTES + (has_table ? TB_BYTES : 0);
     for (int i = 0; i < my_slabs; ++i) {
       const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
       if (!uwait(&empty[s], ph ^ 1, kDevWaitEmpty, i)) break;
-      uint8_t* st = smem + s * C::STAGE_BYTES;
+      uint8_t* st = smem + s * C::X_STAGE_BYTES;
       const int k0 = k_begin + i * SLAB_K;
       if (elect_one()) {
         mbar_arrive_expect_tx(&full[s], stage_bytes);
         tma_load_2d(st, &tmX, k0, m0, &full[s]);
-        if (has_lora) {
-#pragma unroll
-          for (int b = 0; b < RP / 64; ++b) tma_load_2d(st + X_BYTES + b * (SLAB_K * 128), &tmW, b * 64, k0, &full[s]);
-        }
         if (has_table) {
           // one 128-byte piece per 16-column group, 144 bytes apart: the four groups a quad of lanes
           // reads at once then sit in different banks
 #pragma unroll
           for (int gq = 0; gq < 4; ++gq)
-            bulk_load_1d(st + X_BYTES + C::W_BYTES + gq * TB_GROUP_STRIDE, p.table + k0 + gq * 16, 128, &full[s]);
+            bulk_load_1d(st + X_BYTES + gq * TB_GROUP_STRIDE, p.table + k0 + gq * 16, 128, &full[s]);
         }
       }
       __syncwarp();
     }
+  } else if (warp == 2) {
+    // ------------------------------ lora_down producer ------------------------------
+    if (has_lora) {
+      for (int i = 0; i < my_slabs; ++i) {
+        const uint32_t s = i % C::W_STAGES, ph = (i / C::W_STAGES) & 1;
+        if (!uwait(&wempty[s], ph ^ 1, kDevWaitEmpty, 0x50000 + i)) break;
+        uint8_t* st = wring + s * C::W_BYTES;
+        const int k0 = k_begin + i * SLAB_K;
+        if (elect_one()) {
+          mbar_arrive_expect_tx(&wfull[s], C::W_BYTES);
+#pragma unroll
+          for (int b = 0; b < RP / 64; ++b) tma_load_2d(st + b * (SLAB_K * 128), &tmW, b * 64, k0, &wfull[s]);
+        }
+        __syncwarp();
+      }
+    }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     constexpr uint64_t kDescA = smem_desc_base(0, 1024, kSwizzle128B);               // x tile, K-major
-    constexpr uint64_t kDescB = smem_desc_base(SLAB_K * 128, 1024, kSwizzle128B);    // lora_down slab, R-major
+    constexpr uint64_t kDescB = smem_desc_base(SLAB_K * 128, 1024, kSwizzle128B);    // lora_down slab, R-major (its own ring)
     constexpr uint32_t kIdesc = idesc_f16(kBf16, kBf16, TILE_M, RP, false, true);
     bool ok = true;
     for (int i = 0; i < my_slabs && ok; ++i) {
       const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
       if (!uwait(&full[s], ph, kDevWaitFull, i)) { ok = false; break; }
+      const uint32_t sw = i % C::W_STAGES;
+      if (has_lora && !uwait(&wfull[sw], (i / C::W_STAGES) & 1, kDevWaitFull, 0x50000 + i)) { ok = false; break; }
       tc_fence_after_sync();
-      const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
-      const uint32_t b_addr = a_addr + X_BYTES;
+      const uint32_t a_addr = smem_u32(smem + s * C::X_STAGE_BYTES);
+      const uint32_t b_addr = smem_u32(wring + sw * C::W_BYTES);
       if (elect_one()) {
         if (has_lora) {
 #pragma unroll
@@ -225,7 +253,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
             mma_f16<1>(tmem_acc, smem_desc(kDescA, a_addr + j * 32), smem_desc(kDescB, b_addr + j * 2048), kIdesc,
                        (i | j) != 0 ? 1u : 0u);
         }
-        if (has_lora) { tc_commit(&empty[s]); if (i == my_slabs - 1) tc_commit(acc_done); }
+        if (has_lora) { tc_commit(&empty[s]); tc_commit(&wempty[sw]); if (i == my_slabs - 1) tc_commit(acc_done); }
         else mbar_arrive(&empty[s]);
       }
       __syncwarp();
@@ -246,7 +274,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     for (int i = grp; i < my_slabs; i += QUANT_GROUPS) {
       const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
       if (!mbar_wait(&full[s], ph, ctx, kDevWaitFull, 0x10000 + i)) break;
-      const uint8_t* st = smem + s * C::STAGE_BYTES;
+      const uint8_t* st = smem + s * C::X_STAGE_BYTES;
       uint4 raw[2][2];
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
@@ -265,7 +293,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       }
       if (has_table) {
         // {smooth, 1/smooth} of this lane's 16 columns landed with the slab
-        const float4* tb = reinterpret_cast<const float4*>(st + X_BYTES + C::W_BYTES + g * TB_GROUP_STRIDE);
+        const float4* tb = reinterpret_cast<const float4*>(st + X_BYTES + g * TB_GROUP_STRIDE);
         smooth_divide(f[0], tb, use_fdiv);
         smooth_divide(f[1], tb, use_fdiv);
       }
