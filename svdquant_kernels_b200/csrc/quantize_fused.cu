@@ -98,7 +98,8 @@ struct Cfg {
   static constexpr int EPI_COLS = RP / 4 < 32 ? 32 : RP / 4;      // accumulator columns per epilogue warp
   static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the x ring");
   static_assert(STAGES >= QUANT_GROUPS && STAGES % QUANT_GROUPS == 0, "ring depth");
-  static_assert((2 * STAGES + 2 * W_STAGES + 2) * 8 + 64 <= 512, "barrier block");
+  static_assert((2 * STAGES + 2 * W_STAGES + 3) * 8 + 64 <= 512, "barrier block");
+  static_assert(2 * RECV_BYTES <= W_RING_BYTES, "the exchange stages both halves of the accumulator in the lora_down ring");
   static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 };
 
@@ -140,7 +141,8 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   uint64_t* wempty = wfull + C::W_STAGES;      // [W_STAGES]  lora_down slab consumed (MMA)
   uint64_t* acc_done = wempty + C::W_STAGES;   // MMA -> epilogue
   uint64_t* recv_bar = acc_done + 1;           // two K ranks: the peer's partial sums have landed in `recv`
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(recv_bar + 1);
+  uint64_t* ack_bar = recv_bar + 1;            // two K ranks: the peer has received what this CTA sent
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ack_bar + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint32_t* lora_unfit = tmem_slot + 2;        // bf16 form: some LoRA value this CTA wrote does not fit fp16
   float2* scale_lut = reinterpret_cast<float2*>(smem + C::BARS_OFF + 512);   // per scale byte: {2^(2-E), ~1/(4J)}
@@ -171,7 +173,9 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1 + QUANT_WARPS / QUANT_GROUPS); }
     for (int s = 0; s < C::W_STAGES; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wempty[s], 1); }
     mbar_init(acc_done, 1);
-    mbar_init(recv_bar, 2);                    // the peer's two warps that hold this CTA's rows
+    mbar_init(recv_bar, 1);                    // armed below with the bytes of the peer's two copies
+    mbar_init(ack_bar, 1);
+    if (kDirectExchange && ks == 2 && has_lora) mbar_arrive_expect_tx(recv_bar, C::RECV_BYTES);
     fence_barrier_init();
     tma_prefetch_desc(&tmX);
     if (has_lora) tma_prefetch_desc(&tmW);
@@ -183,8 +187,8 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
   qmath::fill_scale_lut(scale_lut, threadIdx.x, NUM_THREADS);
   tc_fence_before_sync();
   __syncthreads();
-  // Two K ranks hand their partial sums to each other with plain remote stores and a remote barrier
-  // arrival, so the partner's barrier must exist before either touches it.  (The CTAs of a cluster
+  // Two K ranks hand their partial sums to each other through the copy engine, counted on the partner's
+  // barrier, so that barrier must exist (and be armed) before either touches it.  (The CTAs of a cluster
   // start together; this costs a fraction of a microsecond, before the wait for the kernel ahead.)
   if (kDirectExchange && ks == 2 && has_lora) cluster_sync_all();
   tc_fence_after_sync();
@@ -330,62 +334,72 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     // Two K ranks (the form for tall activations): CTA k owns rows [32 k, 32 k + 32) of the tile.  The four
     // auxiliary warps do the whole exchange while the quantize warps are still busy with the last slabs:
     // warp w reads rows 16 w .. 16 w + 15 of the accumulator (lanes 0-15 of its quarter of tensor
-    // memory); rows of the partner go straight into the partner's receive buffer (remote shared-memory
-    // stores, then one remote barrier arrival per warp), own rows wait for the partner's two arrivals,
-    // add the two partial sums (two terms: the order does not matter) and leave for global memory.
+    // memory) into the lora_down ring, which is free once the last MMA has retired.  Rows of the partner
+    // then go to the partner's receive buffer with one copy-engine transfer per warp, counted on the
+    // partner's barrier (remote stores by the 16 lanes took 1.3 us of issue slots that the quantize warps
+    // wanted); own rows wait there for the partner's.  Then all four warps add the two partial sums (two
+    // terms: the order does not matter) and write the finished rows out, consecutive lanes taking
+    // consecutive 16 bytes of a row.
     if (warp < AUX_WARPS) {
       constexpr uint32_t RP4 = RP / 4;
+      constexpr uint32_t HALF_BYTES = 16u * RP * 4u;                 // one warp's 16 rows
       const bool ok = __all_sync(0xffffffffu, mbar_wait(acc_done, 0, ctx, kDevWaitAcc, 0)) != 0;
       tc_fence_after_sync();
       const bool mine = static_cast<uint32_t>(warp >> 1) == krank;
       const uint32_t row_local = 16u * (warp & 1) + (lane & 15);     // row within the owner's 32
       const uint32_t taddr = tmem_acc + (static_cast<uint32_t>(warp * 32) << 16);
+      float4* send = reinterpret_cast<float4*>(wring);                // [32 rows][RP / 4], slots as partial_slot
+      float4* own = reinterpret_cast<float4*>(wring + C::RECV_BYTES);
+      float4* dst = mine ? own : send;
+#pragma unroll 1
+      for (int c0 = 0; c0 < RP; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr + c0, v);
+        tmem_ld_wait();
+        if (lane < 16) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            dst[partial_slot(row_local, (c0 >> 2) + j, RP4)] =
+                make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        }
+      }
       if (!mine) {
-        const uint32_t peer_recv = map_to_cta(smem_u32(recv), krank ^ 1u);
-#pragma unroll 1
-        for (int c0 = 0; c0 < RP; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c0, v);
-          tmem_ld_wait();
-          if (lane < 16) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              st_cluster_f4(peer_recv + partial_slot(row_local, (c0 >> 2) + j, RP4) * 16u,
-                            make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]), __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3])));
-          }
-        }
+        fence_proxy_async_smem();                                     // the copy engine reads what the lanes wrote
         __syncwarp();
-        if (lane == 0 && ok) mbar_arrive_cluster(recv_bar, krank ^ 1u);    // release at cluster scope: the stores above are visible first
-      } else {
-        const bool got = __all_sync(0xffffffffu, mbar_wait_cluster(recv_bar, 0, ctx, kDevWaitMisc, 0x40000)) != 0;
-        const size_t gm = static_cast<size_t>(m0) + 32u * krank + row_local;
-#pragma unroll 1
-        for (int c0 = 0; c0 < RP; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr + c0, v);
-          tmem_ld_wait();
-          if (lane < 16 && ok && got) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int c = c0 + 4 * j;
-              if (c < p.R) {
-                const float4 t = recv[partial_slot(row_local, (c0 >> 2) + j, RP4)];
-                const float4 o = make_float4(__uint_as_float(v[4 * j]) + t.x, __uint_as_float(v[4 * j + 1]) + t.y,
-                                             __uint_as_float(v[4 * j + 2]) + t.z, __uint_as_float(v[4 * j + 3]) + t.w);
-                *reinterpret_cast<float4*>(p.lora + gm * p.R + c) = o;
-                if (p.lora16 != nullptr) {
-                  store_lora16x4<T>(p.lora16, gm * p.R + c, static_cast<size_t>(p.M_pad) * p.R, o);
-                  if (kBf16 && !fits_f16(o)) atomicOr(lora_unfit, 1u);
-                }
-              }
-            }
-          }
+        if (lane == 0 && ok) {
+          const uint32_t off = (warp & 1) * HALF_BYTES;
+          bulk_copy_smem_to_cluster(map_to_cta(smem_u32(recv) + off, krank ^ 1u), smem_u32(send) + off, HALF_BYTES,
+                                    map_to_cta(smem_u32(recv_bar), krank ^ 1u));
         }
+      } else {
+        const bool got = __all_sync(0xffffffffu, mbar_wait(recv_bar, 0, ctx, kDevWaitMisc, 0x40000)) != 0;
+        // both halves are here: the partner may give up the memory they were copied from
+        if ((warp & 1) == 0 && lane == 0 && got) mbar_arrive_cluster(ack_bar, krank ^ 1u);
       }
       tc_fence_before_sync();
       asm volatile("bar.sync 3, %0;" ::"n"(AUX_WARPS * 32) : "memory");
-      if (kBf16 && p.lora16 != nullptr && threadIdx.x == 0)
-        lora16_flags(p.lora16, static_cast<size_t>(p.M_pad) * p.R)[m0 / 32 + krank] = *lora_unfit;
+      if (*abort_flag == 0) {
+        const uint32_t r4 = static_cast<uint32_t>(p.R) >> 2;
+        const size_t row0 = static_cast<size_t>(m0) + 32u * krank;
+        for (uint32_t it = threadIdx.x; it < 32u * r4; it += AUX_WARPS * 32) {
+          const uint32_t row = it / r4, c4 = it - row * r4;
+          const uint32_t slot = partial_slot(row, c4, RP4);
+          const float4 a = own[slot], b = recv[slot];
+          const float4 o = make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+          const size_t idx = (row0 + row) * p.R + 4u * c4;
+          *reinterpret_cast<float4*>(p.lora + idx) = o;
+          if (p.lora16 != nullptr) {
+            store_lora16x4<T>(p.lora16, idx, static_cast<size_t>(p.M_pad) * p.R, o);
+            if (kBf16 && !fits_f16(o)) atomicOr(lora_unfit, 1u);
+          }
+        }
+      }
+      if (kBf16 && p.lora16 != nullptr) {
+        asm volatile("bar.sync 3, %0;" ::"n"(AUX_WARPS * 32) : "memory");
+        if (threadIdx.x == 0) lora16_flags(p.lora16, static_cast<size_t>(p.M_pad) * p.R)[m0 / 32 + krank] = *lora_unfit;
+      }
+      // the partner has everything this CTA sent: only then may the memory it was copied from go away
+      if (warp == 0) (void)__all_sync(0xffffffffu, mbar_wait_cluster(ack_bar, 0, ctx, kDevWaitMisc, 0x41000));
     }
   } else if (has_lora) {
     constexpr uint32_t RP4 = RP / 4;

@@ -426,6 +426,14 @@ __device__ __forceinline__ void st_cluster_f4(uint32_t cluster_addr, float4 v) {
   asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
                ::"r"(cluster_addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
+// Copy engine, this CTA's shared memory -> another CTA of the cluster; the bytes are counted on a barrier
+// of the receiving CTA (both destination addresses are cluster addresses from map_to_cta).  The source
+// must stay in place until the receiver has seen its barrier complete and said so.
+__device__ __forceinline__ void bulk_copy_smem_to_cluster(uint32_t dst_cluster_addr, uint32_t src_cta_addr,
+                                                          uint32_t bytes, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster_addr), "r"(src_cta_addr), "r"(bytes), "r"(bar_cluster_addr) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_cluster_u32(uint32_t cluster_addr) {
   uint32_t v;
   asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
