@@ -304,8 +304,8 @@ def _kernel_figures(shape, q_us, g_us, peaks):
 
 def _tp_block(torch, dist, ops, dev, rank, world, timer_iters=60):
     """Column-sharded (tensor-parallel) form on the c4 shape: x replicated, weight rows sharded.
-    fused = svdq_gemm_w4a4_columns (all-gather folded into the GEMM epilogue as plain peer stores,
-    a rank barrier on either side); nccl = local slab GEMM + NCCL all-gather + strided copy."""
+    fused = svdq_gemm_w4a4_columns (all-gather folded into the GEMM epilogue as TMA stores into the peers'
+    copies, a rank barrier on either side); nccl = local slab GEMM + NCCL all-gather + strided copy."""
     from svdquant_kernels_b200 import sharding
     from svdquant_kernels_b200.workloads import CONFIGS, make_inputs
     shape = CONFIGS["c4"]
@@ -332,33 +332,61 @@ def _tp_block(torch, dist, ops, dev, rank, world, timer_iters=60):
     def nccl():
         return sharding.linear_columns(None, lambda _x: local(), N)
 
-    def timed(fn):
+    def bars():
+        lin.handle.barrier(channel=0)
+        lin.handle.barrier(channel=1)
+
+    def timed(fn, iters=timer_iters):
         for _ in range(5):
             fn()
         torch.cuda.synchronize()
         dist.barrier()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(timer_iters + 1)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
         ev[0].record()
-        for i in range(timer_iters):
+        for i in range(iters):
             fn()
             ev[i + 1].record()
         torch.cuda.synchronize()
-        ms = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(timer_iters))
+        ms = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(iters))
         return ms[len(ms) // 2] * 1e3
+
+    def graphed(fn, calls=10):
+        """Device time per call: `calls` calls captured in one CUDA graph, median of 20 replays.  Eager
+        calls of these few-kernel sequences are bound by the Python launch path, not by the GPU."""
+        try:
+            fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(calls):
+                    fn()
+            return timed(g.replay, 20) / calls
+        except Exception:                              # capture refused: the eager figure stands alone
+            torch.cuda.synchronize()
+            return float("nan")
 
     y_f = fused()
     torch.cuda.synchronize()
     same_fused = bool(torch.equal(y_f, y_one))
     same_nccl = bool(torch.equal(nccl(), y_one))
-    t = torch.tensor([timed(local), timed(fused), timed(nccl), 0.0 if same_fused else 1.0, 0.0 if same_nccl else 1.0],
-                     dtype=torch.float64, device=dev)
+    eager = [timed(local), timed(fused), timed(nccl)]
+    graph = [graphed(local), graphed(fused), graphed(bars), graphed(nccl)]
+    same_fused = same_fused and bool(torch.equal(fused(), y_one))
+    t = torch.tensor(eager + graph + [0.0 if same_fused else 1.0, 0.0 if same_nccl else 1.0], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    local_us, fused_us, nccl_us, bad_f, bad_n = t.tolist()
+    local_eager, fused_eager, nccl_eager, local_us, fused_us, bars_us, nccl_us, bad_f, bad_n = t.tolist()
+    if fused_us != fused_us or local_us != local_us:   # no graph figure on some rank
+        local_us, fused_us, bars_us = local_eager, fused_eager, None
+    if nccl_us != nccl_us:
+        nccl_us = nccl_eager
     pushed = M_pad * n * 2 * (world - 1)
     return {
         "workload": f"c4 shape M={M} K={K} N={N} R={R} fp16, x replicated, N sharded {world} ways ({n} columns per rank)",
-        "timing": f"eager calls, CUDA events per call, median of {timer_iters}, max over ranks",
-        "local_gemm_us": local_us, "fused_us": fused_us, "nccl_allgather_us": nccl_us,
+        "timing": "device time per call: 10 calls in one CUDA graph, median of 20 replays, max over ranks; "
+                  f"*_eager_us: Python calls, CUDA events per call, median of {timer_iters} (bound by the launch path)",
+        "local_gemm_us": local_us, "fused_us": fused_us, "rank_barriers_us": bars_us, "nccl_allgather_us": nccl_us,
+        "local_gemm_eager_us": local_eager, "fused_eager_us": fused_eager, "nccl_allgather_eager_us": nccl_eager,
         "bytes_pushed_per_rank": pushed, "fused_push_gbs": pushed / (fused_us * 1e-6) / 1e9,
         "nvlink_measured_gbs_per_direction": 770.0,
         "limiter": "NVLink" if pushed / 770e9 * 1e6 > local_us else "local GEMM + the two rank barriers",

@@ -254,7 +254,7 @@ int svdq_gemm_w4a4_static_ws(const void* act, const void* wgt, const void* ascal
  * Column-sharded (tensor-parallel) form of svdq_gemm_w4a4, one call per GPU: this GPU holds rows
  * [col0, col0 + N) of wgt / wscales / lora_up / wcscales / bias and computes those columns of the
  * [M, N_total] result.  Every finished 32 x 64 strip is written into y_full (this GPU's copy of the
- * whole result) and, with plain stores over NVLink, into the same place of y_full_peers[0 ..
+ * whole result) and, as one TMA store per peer over NVLink, into the same place of y_full_peers[0 ..
  * n_peers-1] (device pointers to the other GPUs' copies, mapped into this process: symmetric
  * memory, CUDA IPC or cuMemMap), so the all-gather the sharding needs rides on the GEMM's epilogue
  * instead of following it.  The caller orders the ranks around the call: nobody may still read its

@@ -52,8 +52,9 @@
 // role from the same words, so all agree on the tile's slab count).
 //
 // Column-sharded form (n_peers > 0): the launch fills N columns of a wider result
-// that every GPU holds in full; each finished strip is also written, with plain
-// 16-byte stores from the staging buffer, into the peers' copies over NVLink.
+// that every GPU holds in full; each finished strip also leaves the staging buffer
+// as one TMA store per peer, into the peers' copies over NVLink (lane stores of 16
+// bytes measured the same: the link, not the store path, sets the pace).
 //
 // Split-K form (SK = true, one CTA per 128 x 128 tile part): for problems with few tiles and a
 // long K, S CTAs share a tile's slabs.  Each parks its fp32 partial tile in a caller-owned
@@ -69,6 +70,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cstdlib>
 #include <type_traits>
 
 namespace svdq {
@@ -115,6 +117,11 @@ struct Cfg {
   static_assert((3 * STAGES + 2 * ACC_STAGES + 2 * SF_BUFS) * 8 + 16 <= 512, "barrier block");
 };
 
+// Column-sharded form: one tensor map per peer's copy of the result (same geometry as this GPU's).
+struct PeerMaps {
+  CUtensorMap m[7];
+};
+
 struct Params {
   const void* wc;       // [N] or null
   const void* bias;     // [N] or null
@@ -123,10 +130,9 @@ struct Params {
   int tiles_m, tiles_n; // in units of (CG*128) x BN
   // Column-sharded (tensor-parallel) form: this launch computes columns [col0, col0 + N) of a
   // [M, y_ld] result that every rank holds in full.  The local copy is written through tmY (built over
-  // the local full matrix); each finished strip is also stored, with plain 16-byte stores straight
-  // from the staging buffer, into the same place of every peer's matrix (peer-mapped memory).
+  // the local full matrix); each finished strip is also stored, by TMA from the same staging buffer,
+  // into the same place of every peer's matrix (peer-mapped memory, one tensor map per peer).
   int col0, y_ld, n_peers;
-  void* y_peer[7];
   // Split-K form (SK kernels only): a tile's slabs are shared by `splits` CTAs; each writes its fp32
   // partial tile to ws_partials[(tile * splits + split) * BM * BN], takes a ticket from
   // ws_tickets[tile], and the CTA that draws the last ticket adds the partials in split order, runs
@@ -174,7 +180,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmLA, const __grid_constant__ CUtensorMap tmLU,
                  const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmSFA,
                  const __grid_constant__ CUtensorMap tmSFB, const __grid_constant__ CUtensorMap tmLAf,
-                 const __grid_constant__ CUtensorMap tmLUf, const Params p) {
+                 const __grid_constant__ CUtensorMap tmLUf, const __grid_constant__ PeerMaps peers, const Params p) {
   using C = Cfg<CG, BN>;
   constexpr bool kBf16 = std::is_same<OutT, __nv_bfloat16>::value;
 
@@ -613,27 +619,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
         if (lane == 0) {
           tma_store_2d(&tmY, buf, p.col0 + n0 + cbase, m0 + quarter * 32);
+          // the same strip into every peer's matrix: the copy engine sends it over NVLink while the warp goes on
+          for (int d = 0; d < p.n_peers; ++d) tma_store_2d(&peers.m[d], buf, p.col0 + n0 + cbase, m0 + quarter * 32);
           tma_store_commit();
-        }
-        if (p.n_peers > 0) {
-          // the strip is 32 rows x 128 bytes in the staging buffer (16-byte chunks XOR-swizzled by row);
-          // eight lanes carry one row, so every store instruction writes four whole 128-byte lines
-          const uint32_t chunk = static_cast<uint32_t>(lane & 7);
-          uint4 part[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const uint32_t r = static_cast<uint32_t>(4 * i + (lane >> 3));
-            part[i] = *reinterpret_cast<const uint4*>(buf + r * 128 + ((chunk ^ (r & 7u)) << 4));
-          }
-          const size_t col = static_cast<size_t>(p.col0 + n0 + cbase) + chunk * 8;
-          for (int d = 0; d < p.n_peers; ++d) {
-            OutT* dst = static_cast<OutT*>(p.y_peer[d]);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const size_t row = static_cast<size_t>(m0 + quarter * 32 + 4 * i + (lane >> 3));
-              *reinterpret_cast<uint4*>(dst + row * p.y_ld + col) = part[i];
-            }
-          }
         }
       }
       }
@@ -708,7 +696,10 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   p.M = M; p.N = N; p.K = K; p.R = R;
   p.tiles_m = M / (gemm::BM * CG); p.tiles_n = N / BN;
   p.col0 = tp.y_ld > 0 ? tp.col0 : 0; p.y_ld = y_ld; p.n_peers = tp.n_peers;
-  for (int d = 0; d < 7; ++d) p.y_peer[d] = d < tp.n_peers ? tp.y_peer[d] : nullptr;
+  gemm::PeerMaps peers;
+  for (int d = 0; d < 7; ++d) peers.m[d] = tmY;
+  for (int d = 0; d < tp.n_peers; ++d)
+    if ((rc = make_tmap_2d(&peers.m[d], tp.y_peer[d], 2, M, y_ld, static_cast<uint64_t>(y_ld) * 2, 32, 64, kTmapSwizzle128)) != SVDQ_OK) return rc;
   p.splits = SK ? splits : 1;
   p.interleave = tp.interleave;
   {
@@ -746,7 +737,7 @@ static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, cons
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, tmLAf, tmLUf, p) != cudaSuccess) return SVDQ_ERR_LAUNCH;
+  if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, tmLAf, tmLUf, peers, p) != cudaSuccess) return SVDQ_ERR_LAUNCH;
   return SVDQ_OK;
 }
 

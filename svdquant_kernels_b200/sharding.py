@@ -74,7 +74,7 @@ class ColumnShardedLinear:
     Every rank holds rows `[col0, col0 + n)` of the weight-side tensors and a `[M, N]` result buffer in
     symmetric memory (torch.distributed._symmetric_memory).  `forward(act, ascales, lora_act)` launches
     the local GEMM in its column-sharded form (`svdq_gemm_w4a4_columns`): each finished 32 x 64 strip
-    goes into the local buffer and, with plain stores over NVLink, into the same place of every peer's
+    goes into the local buffer and, as one TMA store per peer over NVLink, into the same place of every peer's
     buffer.  A barrier over the ranks on the launch stream before the GEMM keeps a fast rank from
     overwriting a buffer a slow peer still reads; one after it makes every peer's strips visible.
     One process per GPU; at most 8 ranks.
