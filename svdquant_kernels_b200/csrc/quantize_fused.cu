@@ -298,8 +298,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
       if (has_table) {
         // {smooth, 1/smooth} of this lane's 16 columns landed with the slab
         const float4* tb = reinterpret_cast<const float4*>(st + X_BYTES + g * TB_GROUP_STRIDE);
-        smooth_divide(f[0], tb, use_fdiv);
-        smooth_divide(f[1], tb, use_fdiv);
+        qmath::smooth_divide2(f[0], f[1], tb, use_fdiv);
       }
       // Hand the stage back.  The ring was read through the generic proxy and will be overwritten
       // through the async proxy (TMA); mbarrier arrivals are performed by a separate unit and do not

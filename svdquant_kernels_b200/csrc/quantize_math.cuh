@@ -81,6 +81,31 @@ __device__ __forceinline__ void smooth_divide(float2 (&f)[8], const float4* tb, 
   }
 }
 
+// Two rows of the same 16 columns: every table entry is loaded once.  A 16-byte shared-memory load costs
+// four wavefronts of the load/store unit however many lanes share its address, and that unit (x loads, table
+// loads, the stores, the MMA's operand reads and the TMA's writes all pass through it) is what the fused
+// quantizer saturates.
+__device__ __forceinline__ void smooth_divide2(float2 (&f0)[8], float2 (&f1)[8], const float4* tb, bool use_fdiv) {
+  if (!use_fdiv) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 t = tb[j];
+      const float2 hi = make_float2(t.x, t.y), lo = make_float2(t.z, t.w);
+      f0[j] = __ffma2_rn(f0[j], hi, __fmul2_rn(f0[j], lo));
+      f1[j] = __ffma2_rn(f1[j], hi, __fmul2_rn(f1[j], lo));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float4 t = tb[j];
+      f0[j].x = __fadd_rn(__fdiv_rn(f0[j].x, t.x), 0.0f);          // an underflow to -0 counts as +0
+      f0[j].y = __fadd_rn(__fdiv_rn(f0[j].y, t.y), 0.0f);
+      f1[j].x = __fadd_rn(__fdiv_rn(f1[j].x, t.x), 0.0f);
+      f1[j].y = __fadd_rn(__fdiv_rn(f1[j].y, t.y), 0.0f);
+    }
+  }
+}
+
 // Table entry of one column pair (see above); `exact_divide` selects the {s0, s1} form.
 __device__ __forceinline__ float4 smooth_table_entry(float s0, float s1, bool exact_divide) {
   if (exact_divide) return make_float4(s0, s1, 0.0f, 0.0f);
