@@ -292,6 +292,15 @@ int svdq_device_status(unsigned int out[4]);
 int svdq_selftest_wait_expiry(unsigned long long limit_ns, unsigned int* seen_device, void* stream);
 
 /*
+ * Self-test of the division svdq_gemm_w4a4_next uses for y / smooth_next: for every fp32 significand of
+ * the dividend (2^23) and every 11-bit significand of the divisor (2^10, which covers fp16 and bf16) it
+ * compares the three-step quotient through the correctly rounded reciprocal with the IEEE quotient and
+ * counts the pairs that differ into *mismatches_device (8 bytes of device memory; expected 0).  About
+ * 10 ms of GPU time.  No counterpart in the reference (which divides in PyTorch).
+ */
+int svdq_selftest_divide(unsigned long long* mismatches_device, void* stream);
+
+/*
  * Whole linear from HOST buffers: copies x to the device, runs quantizer and
  * GEMM on weights already resident in the plan, copies y back and waits.
  * A plan owns its device buffers (allocated once in svdq_linear_plan_create).

@@ -44,6 +44,7 @@ SIGNATURES = {
     "svdq_gemm_w4a4_supported": (c_int, [c_int, c_int, c_int, c_int]),
     "svdq_device_status": (c_int, [POINTER(c_uint)]),
     "svdq_selftest_wait_expiry": (c_int, [c_ulonglong, c_void_p, c_void_p]),
+    "svdq_selftest_divide": (c_int, [c_void_p, c_void_p]),
     "svdq_linear_plan_create": (c_int, [POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int] + [c_void_p] * 7),
     "svdq_linear_plan_forward_host": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),
     "svdq_linear_plan_submit": (c_int, [c_void_p, c_void_p, c_void_p, c_int]),

@@ -354,6 +354,29 @@ int svdq_selftest_wait_expiry(unsigned long long limit_ns, unsigned int* seen_de
   return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;
 }
 
+// Every fp32 significand of a (2^23, a in [1, 2)) against every 11-bit significand of s (2^10, s in [1, 2)):
+// qmath::divide_by_constant2 with r = __frcp_rn(s) must equal __fdiv_rn(a, s).  Block b takes s = 1 + b / 1024.
+__global__ void divide_selftest_kernel(unsigned long long* mismatches) {
+  const float sv = __uint_as_float(0x3f800000u | (static_cast<uint32_t>(blockIdx.x) << 13));
+  const float r = __frcp_rn(sv);
+  const float2 ns = make_float2(-sv, -sv), rr = make_float2(r, r);
+  unsigned int bad = 0;
+  for (uint32_t m = threadIdx.x * 2u; m < (1u << 23); m += blockDim.x * 2u) {
+    const float a0 = __uint_as_float(0x3f800000u | m), a1 = __uint_as_float(0x3f800000u | (m + 1u));
+    const float2 q = svdq::qmath::divide_by_constant2(make_float2(a0, a1), ns, rr);
+    bad += (q.x != __fdiv_rn(a0, sv)) + (q.y != __fdiv_rn(a1, sv));
+  }
+  if (bad) atomicAdd(mismatches, static_cast<unsigned long long>(bad));
+}
+
+int svdq_selftest_divide(unsigned long long* mismatches_device, void* stream) {
+  if (mismatches_device == nullptr) return SVDQ_ERR_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(mismatches_device, 0, sizeof(unsigned long long), st) != cudaSuccess) return SVDQ_ERR_CUDA;
+  divide_selftest_kernel<<<1024, 1024, 0, st>>>(mismatches_device);
+  return cudaGetLastError() == cudaSuccess ? SVDQ_OK : SVDQ_ERR_LAUNCH;
+}
+
 // ---------------------------------------------------------------------------
 // host-buffer plan
 // ---------------------------------------------------------------------------

@@ -86,7 +86,7 @@ constexpr int SF_WARPS = 2;       // scale copiers: each takes two of a slab's f
 constexpr int NUM_THREADS = (EPI_WARPS + 2 + SF_WARPS) * 32;
 constexpr int STORE_BUF_BYTES = 32 * 128;  // one 32-row x 64-column strip of y
 
-template <int CG, int BN>
+template <int CG, int BN, bool NEXT = false>
 struct Cfg {
   static constexpr int B_ROWS = BN / CG;                           // rows of B this CTA loads
   static constexpr int B_BYTES = B_ROWS * 128;
@@ -99,7 +99,10 @@ struct Cfg {
   static constexpr int GROUPS_PER_WARP = BN / 128;                 // 64-column strips each epilogue warp handles per tile
   static constexpr int STORE_BUFS = 1;
   static constexpr int STORE_BYTES = EPI_WARPS * STORE_BUFS * STORE_BUF_BYTES;
-  static constexpr int TAIL_BYTES = 3072 /*affine: wcscales, bias, smooth_next*/ + 512 /*barriers*/;
+  // per-column rows of the current tile: wcscales, bias and, for the next layer's quantisation, -smooth_next and
+  // 1 / smooth_next (that fourth kilobyte would cost the plain 256 x 256 form its fifth ring stage)
+  static constexpr int AFFINE_BYTES = NEXT ? 4096 : 3072;
+  static constexpr int TAIL_BYTES = AFFINE_BYTES + 512 /*barriers*/;
   static constexpr int STAGES_RAW = (232448 - 1024 - STORE_BYTES - TAIL_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
   static constexpr int SFA_COLS = 16;                 // 4 k-blocks x 4 columns
@@ -174,6 +177,53 @@ template <typename T> __device__ __forceinline__ float as_f32(T v);
 template <> __device__ __forceinline__ float as_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float as_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+// Next layer's quantisation of one 16-column group of one row: the 16 fp32 results (already scaled and
+// biased) are divided by smooth_next and packed as NVFP4.  ns4 / r4: the group's four entries of the
+// -smooth_next and 1 / smooth_next rows.  Returns {codes 0-7, codes 8-15, scale byte, -}.
+// Not inlined on purpose: the epilogue calls it eight times per tile from fully unrolled code (the
+// accumulator lives in registers, which only constant indices can address), and eight copies of the
+// division, the scale and both code paths made the epilogue too large for the instruction cache (the top
+// stall reason was "no instruction", at 17 % issue utilisation).
+__device__ __noinline__ uint4 next_group_codes(float2 a0, float2 a1, float2 a2, float2 a3, float2 a4, float2 a5,
+                                               float2 a6, float2 a7, const float4* ns4, const float4* r4, int tile_fdiv) {
+  const float2 a[8] = {a0, a1, a2, a3, a4, a5, a6, a7};
+  float2 q[8];
+  // IEEE divide of the uncast fp32 values, as the reference does; + 0 turns a -0 quotient into +0 (the
+  // reference gives a zero the sign bit only when the value tests < 0)
+  auto divide_ieee = [&]() {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 ns = ns4[j];
+      q[2 * j] = make_float2(__fadd_rn(__fdiv_rn(a[2 * j].x, -ns.x), 0.0f), __fadd_rn(__fdiv_rn(a[2 * j].y, -ns.y), 0.0f));
+      q[2 * j + 1] = make_float2(__fadd_rn(__fdiv_rn(a[2 * j + 1].x, -ns.z), 0.0f), __fadd_rn(__fdiv_rn(a[2 * j + 1].y, -ns.w), 0.0f));
+    }
+  };
+  if (!tile_fdiv) {
+    // the same quotients in three packed instructions per pair (qmath::divide_by_constant2)
+    const float2 zero = make_float2(0.0f, 0.0f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float4 ns = ns4[j], r = r4[j];
+      q[2 * j] = __fadd2_rn(qmath::divide_by_constant2(a[2 * j], make_float2(ns.x, ns.y), make_float2(r.x, r.y)), zero);
+      q[2 * j + 1] = __fadd2_rn(qmath::divide_by_constant2(a[2 * j + 1], make_float2(ns.z, ns.w), make_float2(r.z, r.w)), zero);
+    }
+  } else {
+    divide_ieee();
+  }
+  uint32_t sb = qmath::group_scale_byte(q);
+  if (!tile_fdiv && (sb == 0u || sb >= 0x7Eu)) {
+    // Scale byte 0 or 448: a group of tiny or of huge values, where the three-step quotient may have under-
+    // or overflowed on the way.  (With a byte in between, the group's largest quotient lies in [2^-10, 2700):
+    // every operand that can reach a rounding bound of a code is far from both ends of the range, and the
+    // quotients that matter are exact.)
+    divide_ieee();
+    sb = qmath::group_scale_byte(q);
+  }
+  uint32_t lo, hi;
+  qmath::quantize_group_with(q, sb, lo, hi);
+  return make_uint4(lo, hi, sb, 0u);
+}
+
 template <int CG, int BN, typename OutT, bool SK = false, bool NEXT = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -181,7 +231,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmY, const __grid_constant__ CUtensorMap tmSFA,
                  const __grid_constant__ CUtensorMap tmSFB, const __grid_constant__ CUtensorMap tmLAf,
                  const __grid_constant__ CUtensorMap tmLUf, const __grid_constant__ PeerMaps peers, const Params p) {
-  using C = Cfg<CG, BN>;
+  using C = Cfg<CG, BN, NEXT>;
   constexpr bool kBf16 = std::is_same<OutT, __nv_bfloat16>::value;
 
   extern __shared__ uint8_t smem_raw[];
@@ -190,8 +240,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* store_bufs = smem + C::STAGES * C::STAGE_BYTES;        // 1024-aligned: every stage is a multiple of 1 KB
   uint8_t* tail = store_bufs + C::STORE_BYTES;
-  float* affine = reinterpret_cast<float*>(tail);                 // [3][BN] : wcscales, bias, smooth_next of the current tile
-  uint64_t* bars = reinterpret_cast<uint64_t*>(tail + 3072);
+  float* affine = reinterpret_cast<float*>(tail);                 // [3 or 4][BN] : wcscales, bias, -smooth_next, 1/smooth_next of the current tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail + C::AFFINE_BYTES);
   uint64_t* full = bars;                                          // [STAGES]     A / B (or LoRA) operands landed (leader CTA's copy is used)
   uint64_t* empty = bars + C::STAGES;                             // [STAGES]     stage consumed by the MMAs (per CTA)
   uint64_t* full_sf = bars + 2 * C::STAGES;                       // [STAGES]     the stage's scale atoms landed (leader's copy)
@@ -476,12 +526,29 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int m0 = (mb * CG + rank) * BM, n0 = nb * BN;
       const uint32_t as = tcount % C::ACC_STAGES, aph = (tcount / C::ACC_STAGES) & 1;
       // stage this tile's per-column affine terms (the previous tile's readers are past the barrier below)
+      [[maybe_unused]] bool odd_smooth = false;     // NEXT: some smooth_next of this tile is outside [2^-20, 2^20]
       for (int c = threadIdx.x; c < BN; c += EPI_WARPS * 32) {
         affine[c] = wc != nullptr ? as_f32<OutT>(wc[n0 + c]) : 1.0f;
         affine[BN + c] = bias != nullptr ? as_f32<OutT>(bias[n0 + c]) : 0.0f;
-        if constexpr (NEXT) affine[2 * BN + c] = as_f32<OutT>(static_cast<const OutT*>(p.smooth_next)[n0 + c]);
+        if constexpr (NEXT) {
+          const float sv = as_f32<OutT>(static_cast<const OutT*>(p.smooth_next)[n0 + c]);
+          affine[2 * BN + c] = -sv;
+          affine[3 * BN + c] = __frcp_rn(sv);
+          odd_smooth |= !(sv >= 9.5367431640625e-07f && sv <= 1048576.0f);      // also zero, negative, NaN
+        }
       }
-      asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+      // NEXT: the tile divides with __fdiv_rn if any of its columns asks for it (the same verdict in all warps)
+      [[maybe_unused]] bool tile_fdiv = false;
+      if constexpr (NEXT) {
+        uint32_t any_odd;
+        asm volatile(
+            "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\t"
+            "bar.red.or.pred q, 1, %2, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+            : "=r"(any_odd) : "r"(odd_smooth ? 1u : 0u), "n"(EPI_WARPS * 32) : "memory");
+        tile_fdiv = any_odd != 0;
+      } else {
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_WARPS * 32) : "memory");
+      }
       if (!mbar_wait(&acc_full[as], aph, ctx, kDevWaitAcc, tcount)) ok = false;
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + as * BN + chalf * (BN / 2);
@@ -567,12 +634,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const float4* wc4 = reinterpret_cast<const float4*>(affine + cbase + hc * 32);
           const float4* bs4 = reinterpret_cast<const float4*>(affine + BN + cbase + hc * 32);
           uint32_t o[16];
-          [[maybe_unused]] float2 qf[8];      // NEXT: the 16 values of the current column group, divided by smooth_next
+          [[maybe_unused]] float2 qf[8];      // NEXT: the 16 values of the current column group
           [[maybe_unused]] uint32_t qcodes[4], qscales[2];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float a0 = __uint_as_float(v[g][hc][4 * i]), a1 = __uint_as_float(v[g][hc][4 * i + 1]);
-            float a2 = __uint_as_float(v[g][hc][4 * i + 2]), a3 = __uint_as_float(v[g][hc][4 * i + 3]);
+          // the four fp32 results of columns 4 i .. 4 i + 3 of this half strip
+          auto affine_at = [&](int i, float& a0, float& a1, float& a2, float& a3) {
+            a0 = __uint_as_float(v[g][hc][4 * i]); a1 = __uint_as_float(v[g][hc][4 * i + 1]);
+            a2 = __uint_as_float(v[g][hc][4 * i + 2]); a3 = __uint_as_float(v[g][hc][4 * i + 3]);
             if (wc != nullptr) {
               const float4 w4 = wc4[i];
               a0 = __fmul_rn(a0, w4.x); a1 = __fmul_rn(a1, w4.y); a2 = __fmul_rn(a2, w4.z); a3 = __fmul_rn(a3, w4.w);
@@ -581,16 +648,23 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               const float4 b4 = bs4[i];
               a0 = __fadd_rn(a0, b4.x); a1 = __fadd_rn(a1, b4.y); a2 = __fadd_rn(a2, b4.z); a3 = __fadd_rn(a3, b4.w);
             }
+          };
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float a0, a1, a2, a3;
+            affine_at(i, a0, a1, a2, a3);
             o[2 * i] = pack2f<OutT>(a0, a1);
             o[2 * i + 1] = pack2f<OutT>(a2, a3);
             if constexpr (NEXT) {
-              // IEEE divide of the uncast fp32 value, as the reference does; + 0 turns a -0 quotient into
-              // +0 (the reference gives a zero the sign bit only when the value tests < 0)
-              const float4 s4 = reinterpret_cast<const float4*>(affine + 2 * BN + cbase + hc * 32)[i];
-              qf[2 * (i & 3)] = make_float2(__fadd_rn(__fdiv_rn(a0, s4.x), 0.0f), __fadd_rn(__fdiv_rn(a1, s4.y), 0.0f));
-              qf[2 * (i & 3) + 1] = make_float2(__fadd_rn(__fdiv_rn(a2, s4.z), 0.0f), __fadd_rn(__fdiv_rn(a3, s4.w), 0.0f));
-              if ((i & 3) == 3)
-                qmath::quantize_group(qf, nullptr, qcodes[2 * (i >> 2)], qcodes[2 * (i >> 2) + 1], qscales[i >> 2]);
+              qf[2 * (i & 3)] = make_float2(a0, a1);
+              qf[2 * (i & 3) + 1] = make_float2(a2, a3);
+              if ((i & 3) == 3) {
+                const int e4 = (cbase + hc * 32) / 4 + (i - 3);      // float4 index of the group's first column
+                const uint4 r = next_group_codes(qf[0], qf[1], qf[2], qf[3], qf[4], qf[5], qf[6], qf[7],
+                                                 reinterpret_cast<const float4*>(affine + 2 * BN) + e4,
+                                                 reinterpret_cast<const float4*>(affine + 3 * BN) + e4, tile_fdiv ? 1 : 0);
+                qcodes[2 * (i >> 2)] = r.x; qcodes[2 * (i >> 2) + 1] = r.y; qscales[i >> 2] = r.z;
+              }
             }
           }
           if constexpr (NEXT) {
@@ -663,7 +737,7 @@ template <int CG, int BN, typename OutT, bool SK = false, bool NEXT = false>
 static int launch_gemm_t(const void* act, const void* wgt, const void* sfa, const void* sfb, const void* la,
                          const void* lu, const void* lu_f16, const void* wc, const void* bias, void* y, int M, int N,
                          int K, int R, const GemmTp& tp, cudaStream_t stream, int splits = 1) {
-  using C = gemm::Cfg<CG, BN>;
+  using C = gemm::Cfg<CG, BN, NEXT>;
   constexpr bool kBf16 = std::is_same<OutT, __nv_bfloat16>::value;
   CUtensorMap tmA, tmB, tmLA, tmLU, tmY, tmSFA, tmSFB, tmLAf, tmLUf;
   int rc;

@@ -194,6 +194,25 @@ __device__ __forceinline__ void group_codes_compare(const float2 (&f)[8], uint32
   code_lo = lo; code_hi = hi;
 }
 
+// Division by a per-column constant with its reciprocal at hand: q0 = RN(a r), e = a - s q0 (exact in one
+// fma), q = RN(q0 + e r).  With r = RN(1 / s) this is the correctly rounded a / s whenever nothing over- or
+// underflows on the way (Markstein's correction step; it needs a correctly rounded reciprocal and a divisor
+// whose significand is not all ones, which a 16-bit s cannot be).  svdq_selftest_divide checks it against
+// __fdiv_rn for every fp32 significand of a and every 11-bit significand of s; powers of two scale through
+// all three steps exactly.  Arguments: the pair of dividends, the NEGATED divisors and the reciprocals.
+__device__ __forceinline__ float2 divide_by_constant2(float2 a, float2 neg_s, float2 r) {
+  const float2 q0 = __fmul2_rn(a, r);
+  const float2 e = __ffma2_rn(neg_s, q0, a);
+  return __ffma2_rn(e, r, q0);
+}
+
+// quantize_group with the scale byte already worked out
+__device__ __forceinline__ void quantize_group_with(float2 (&f)[8], uint32_t sb, uint32_t& code_lo, uint32_t& code_hi) {
+  const float2 k = scale_constants(sb);
+  if (k.x != 0.0f) group_codes_fast(f, k, code_lo, code_hi);
+  else group_codes_compare(f, sb, code_lo, code_hi);
+}
+
 // One 16-element group (smoothed, fp32): amax, scale byte, eight code bytes.  scale_lut: the table
 // fill_scale_lut made in shared memory, or null to work the two constants out on the spot.
 __device__ __forceinline__ void quantize_group(float2 (&f)[8], const float2* scale_lut,

@@ -251,7 +251,7 @@ def test_split_k_is_deterministic():
 # ------------------------------------------------------------------------------------------------
 # next-layer quantisation in the epilogue (smooth_next -> qout, oscales; baseline/kernels/gemm_w4a4/ref.py:80-87)
 # ------------------------------------------------------------------------------------------------
-def _next_case(M, K, N, R, dtype, seed, tiler=None, wc=True, bias=True):
+def _next_case(M, K, N, R, dtype, seed, tiler=None, wc=True, bias=True, edit=None):
     ops = _ops()
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(M, K, generator=g)
@@ -264,6 +264,8 @@ def _next_case(M, K, N, R, dtype, seed, tiler=None, wc=True, bias=True):
     b = (torch.randn(N, generator=g) * 0.01).to(dtype) if bias else None
     c = (torch.rand(N, generator=g) + 0.5).to(dtype) if wc else None
     sn = (torch.rand(N, generator=g) * 1.5 + 0.25).to(dtype)
+    if edit is not None:
+        b, c, sn = edit(b, c, sn)
     dev = "cuda"
     act, asc, la = ops.quantize_w4a4_act_fuse_lora(x.to(dev), ld.to(dev), sm.to(dev))
     wgt, wsc = ops.quantize_nvfp4_rows(w.to(dev), pad_size=1)
@@ -294,6 +296,48 @@ def test_next_layer_codes_are_bit_exact_where_y_is_exact(dtype, tiler):
     q, s, o_q, o_s = _next_case(256, 256, 256, 0, dtype, seed=41, tiler=tiler)
     assert (s == o_s).all(), "scale bytes differ"
     assert (q == o_q).all(), "code bytes differ"
+
+
+def _tiny_and_huge_groups(b, c, sn):
+    """Columns 0-63: y scaled down to about 1e-9 (scale byte 0: everything that is not zero saturates);
+    columns 64-127: divided by 2^-14 (quotients in the thousands: the 448 clamp); the rest as before."""
+    b, c, sn = b.clone(), c.clone(), sn.clone()
+    c[:64] = 2.0 ** -24
+    b[:64] = 0
+    sn[64:128] = 2.0 ** -14
+    return b, c, sn
+
+
+def _odd_smooth_next(b, c, sn):
+    """One divisor outside [2^-20, 2^20] (fp16: the smallest normal, 2^-14, is inside, so a subnormal;
+    bf16: 2^-30), which sends its tile down the IEEE-divide path; tiles without it keep the short one."""
+    sn = sn.clone()
+    sn[5] = 2.0 ** -24 if sn.dtype == torch.float16 else 2.0 ** -30
+    return b, c, sn
+
+
+@pytest.mark.parametrize("edit", [_tiny_and_huge_groups, _odd_smooth_next])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_next_layer_division_edge_cases_are_bit_exact(dtype, edit):
+    """The epilogue divides by smooth_next in three steps through the reciprocal and falls back to the IEEE
+    divide for a group whose scale byte is 0 or the 448 clamp, and for a tile with a divisor outside
+    [2^-20, 2^20]; all of these must still match the oracle bit for bit where y is exact."""
+    q, s, o_q, o_s = _next_case(256, 256, 512, 0, dtype, seed=47, edit=edit)
+    assert (s == o_s).all(), "scale bytes differ"
+    assert (q == o_q).all(), "code bytes differ"
+    if edit is _tiny_and_huge_groups:
+        assert (o_s[:4] == 0).mean() > 0.5 and (o_s[4:8] == 0x7E).mean() > 0.5, "the case does not reach the two fallbacks"
+
+
+def test_three_step_division_equals_ieee_division_for_every_significand_pair():
+    """svdq_selftest_divide: 2^23 dividend significands x 2^10 divisor significands, on the device."""
+    from svdquant_kernels_b200 import _lib
+    lib = _lib.load()
+    out = torch.full((1,), -1, dtype=torch.int64, device="cuda")
+    rc = lib.svdq_selftest_divide(out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(out.item()) == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
