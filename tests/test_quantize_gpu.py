@@ -106,6 +106,15 @@ def test_fused_matches_oracle(M, K, R, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("R", [8, 40, 96, 136, 256])
+def test_two_rank_exchange_at_every_rank_width(R, dtype):
+    """37 to 74 row tiles run as clusters of two K ranks, which hand each other the partial LoRA sums of 32
+    rows through the copy engine; ranks that do not fill the accumulator's width, and the widest one."""
+    x, ld, sm = _inputs(2400, 640, R, dtype, 17 + R)
+    _check(x, ld, sm, FUSED, 256)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("M,K,R,tm,ks", [(512, 512, 32, 128, 4), (512, 1024, 128, 256, 2), (1024, 1024, 64, 256, 8),
                                          (300, 640, 16, 128, 2), (256, 256, 0, 128, 1), (700, 2560, 128, 256, 1),
                                          (2000, 1536, 128, 128, 4), (2304, 960, 104, 256, 8), (256, 15360, 128, 256, 8),
