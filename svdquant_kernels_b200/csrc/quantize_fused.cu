@@ -370,13 +370,14 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
           bulk_copy_smem_to_cluster(map_to_cta(smem_u32(recv) + off, krank ^ 1u), smem_u32(send) + off, HALF_BYTES,
                                     map_to_cta(smem_u32(recv_bar), krank ^ 1u));
         }
-      } else {
-        const bool got = __all_sync(0xffffffffu, mbar_wait(recv_bar, 0, ctx, kDevWaitMisc, 0x40000)) != 0;
-        // both halves are here: the partner may give up the memory they were copied from
-        if ((warp & 1) == 0 && lane == 0 && got) mbar_arrive_cluster(ack_bar, krank ^ 1u);
       }
       tc_fence_before_sync();
-      asm volatile("bar.sync 3, %0;" ::"n"(AUX_WARPS * 32) : "memory");
+      asm volatile("bar.sync 3, %0;" ::"n"(AUX_WARPS * 32) : "memory");       // own rows are staged
+      // Every thread that will read the receive buffer observes the barrier itself: that is what makes
+      // the copy engine's writes visible to it.
+      const bool got = __all_sync(0xffffffffu, mbar_wait(recv_bar, 0, ctx, kDevWaitMisc, 0x40000)) != 0;
+      // both halves are here: the partner may give up the memory they were copied from
+      if (warp == 0 && lane == 0 && got) mbar_arrive_cluster(ack_bar, krank ^ 1u);
       if (*abort_flag == 0) {
         const uint32_t r4 = static_cast<uint32_t>(p.R) >> 2;
         const size_t row0 = static_cast<size_t>(m0) + 32u * krank;
