@@ -173,8 +173,11 @@ def _oracle_step(shape, rows):
 
     def step():
         act, asc, la = O.quantize_w4a4_act_fuse_lora(xb, ldb, smb, name)
-        return O.gemm_w4a4(act, wgt, asc, wsc, la, lub, wcb, bb, name)[0]
+        y_bits, y_f32 = O.gemm_w4a4(act, wgt, asc, wsc, la, lub, wcb, bb, name)[:2]
+        step.last = (act, asc, la, y_bits, y_f32)
+        return y_bits
 
+    step.inputs = inp
     return step, name
 
 
@@ -635,16 +638,45 @@ def run_ours(args):
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(shape, args)
+        line["parity"] = line["cpu_baseline"].pop("parity")
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
+def _parity(step, name):
+    """The product's two operators on the inputs the CPU oracle has just been timed on, against the
+    oracle's outputs of its last pass: codes and scales bit for bit, lora_act and y by relative L2 norm
+    (the tolerance of both is 1e-3)."""
+    import numpy as np
+    import torch
+    from oracle import nvfp4_oracle as O
+    from svdquant_kernels_b200 import ops
+    inp = step.inputs
+    o_act, o_asc, o_la, o_ybits, o_y = step.last
+    dev = torch.device("cuda", torch.cuda.current_device())
+    act, asc, la = ops.quantize_w4a4_act_fuse_lora(inp.x.to(dev), inp.lora_down.to(dev), inp.smooth.to(dev))
+    wgt, wsc = ops.quantize_nvfp4_rows(inp.w.to(dev), pad_size=1)
+    y = ops.gemm_w4a4(act, wgt, asc, wsc, la, inp.lora_up.to(dev), inp.wcscales.to(dev), inp.bias.to(dev), inp.x.dtype)
+    torch.cuda.synchronize()
+    y_f32 = y.float().cpu().numpy()
+    return {
+        "against": "the CPU oracle's outputs on the same inputs (all rows of the cpu_baseline sample)",
+        "codes_bit_exact": bool((act.cpu().numpy() == o_act).all()),
+        "scales_bit_exact": bool((asc.view(torch.uint8).cpu().numpy() == o_asc).all()),
+        "lora_act_rel_l2": O.rel_l2(la.cpu().numpy(), o_la),
+        "y_rel_l2": O.rel_l2(y_f32, O.bits_to_f32(o_ybits, name)),
+        "y_rel_l2_vs_uncast_fp32": O.rel_l2(y_f32, o_y),
+        "tolerance_rel_l2": 1e-3,
+    }
+
+
 def cpu_baseline(shape, args):
-    """The oracle on this box's host cores, all rows of the same workload, for about ten seconds."""
+    """The oracle on this box's host cores, all rows of the same workload, for about ten seconds; then
+    the parity of the product's outputs with the oracle's on those inputs."""
     rows = shape.M if args.cpu_rows <= 0 else min(shape.M, args.cpu_rows)
-    step, _ = _oracle_step(shape, rows)
+    step, name = _oracle_step(shape, rows)
     step()
     t0 = time.perf_counter()
     reps = 0
@@ -654,8 +686,10 @@ def cpu_baseline(shape, args):
     dt = (time.perf_counter() - t0) / reps
     m_pad = -(-rows // 256) * 256
     what = f"all {rows} rows" if rows == shape.M else f"the first {rows} of {shape.M} rows"
-    return {"value": 2.0 * m_pad * shape.N * shape.K / dt / 1e12, "unit": "TFLOP/s", "cores": _blas_threads(), "kind": "port",
-            "sample": f"{reps} passes over {what} (quantizer + GEMM oracle, numpy/BLAS), {dt:.2f} s each"}
+    out = {"value": 2.0 * m_pad * shape.N * shape.K / dt / 1e12, "unit": "TFLOP/s", "cores": _blas_threads(), "kind": "port",
+           "sample": f"{reps} passes over {what} (quantizer + GEMM oracle, numpy/BLAS), {dt:.2f} s each"}
+    out["parity"] = _parity(step, name)
+    return out
 
 
 def _claim_stdout():
