@@ -287,6 +287,17 @@ class DeviceLinear:
         self.quant(i)
         return self.gemm(i)
 
+    def gemm_next(self, i):
+        """The GEMM that also quantises its result for a following linear (smooth_next -> qout, oscales)."""
+        i %= self.nsets
+        if not hasattr(self, "sn"):
+            torch = self.torch
+            g = torch.Generator().manual_seed(99)
+            self.sn = (torch.rand(self.shape.N, generator=g) * 1.5 + 0.25).to(self.shape.dtype).to(self.wgt.device)
+        act, asc, la = self.q[i]
+        return self.ops.gemm_w4a4(act, self.wgt, asc, self.wsc, la, self.lu, self.wc, self.bias, self.shape.dtype,
+                                  smooth_next=self.sn)
+
     def capture(self, fn, n):
         g = self.torch.cuda.CUDAGraph()
         with self.torch.cuda.graph(g):
@@ -433,6 +444,8 @@ def run_ours(args):
         # for profilers: a few more plain launches and nothing else (no graphs, no JSON line)
         for i in range(args.eager_only):
             lin.step(i)
+            if args.next_layer:
+                lin.gemm_next(i)
         torch.cuda.synchronize()
         sampler.stop()
         print(f"eager-only: {warm + args.eager_only} steps done, status {_lib.device_status()}", file=sys.stderr)
@@ -495,6 +508,15 @@ def run_ours(args):
     ms_per_step = r_all["median_ms"] / steps
     q_us = r_q["median_ms"] / steps * 1e3
     g_us = r_g["median_ms"] / steps * 1e3
+    # the GEMM with the next layer's quantisation fused into its epilogue (a graph of its own; its outputs
+    # are allocated inside the capture, from the graph's pool)
+    next_us = None
+    if rank == 0 and world == 1 and not args.no_other_configs:
+        lin.gemm_next(0)
+        torch.cuda.synchronize()
+        g_n = lin.capture(lin.gemm_next, steps)
+        next_us = timer.time(g_n)["median_ms"] / steps * 1e3
+        del g_n
 
     # ---- end to end: host buffers through the C-ABI plan ----
     inp = lin.inp
@@ -599,6 +621,8 @@ def run_ours(args):
         "eager_api_note": "wall per step of back-to-back Python calls of the two operators (no graphs), outputs reused through out=",
         "ms_per_step_x_sm_mhz": ms_per_step * (clocks.get("sm_mhz") or 0),
     }
+    if next_us is not None:
+        config["gemm_with_next_layer_quantisation_us"] = next_us
     if per_rank is not None:
         config["per_rank_ms_q_us_g_us"] = per_rank
     if other is not None:
@@ -715,6 +739,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-other-configs", action="store_true", help="skip the per-kernel figures of c2..c4")
     ap.add_argument("--no-tp", action="store_true", help="skip the tensor-parallel block (N > 1)")
+    ap.add_argument("--next-layer", action="store_true", help="with --eager-only: each step also runs the GEMM with the next layer's quantisation in its epilogue")
     ap.add_argument("--eager-only", type=int, default=0, help="after warm-up run this many plain launches of each kernel and exit (for profilers)")
     args = ap.parse_args()
     if args.steps < 1:
