@@ -68,7 +68,7 @@ constexpr int QUANT_WARPS = 4 * QUANT_GROUPS;
 #define SVDQ_DIRECT_EXCHANGE 1
 #endif
 constexpr bool kDirectExchange = SVDQ_DIRECT_EXCHANGE != 0;
-constexpr int AUX_WARPS = 4;                // producer, MMA issuer, two helpers; with two K ranks they exchange the LoRA sums
+constexpr int AUX_WARPS = 4;                // x producer, MMA issuer (even slabs), lora_down producer, MMA issuer (odd slabs); with two K ranks they exchange the LoRA sums
 constexpr int NUM_THREADS = (AUX_WARPS + QUANT_WARPS) * 32;
 constexpr int TB_BYTES = SLAB_K * 8;       // {smooth, 1/smooth} of a slab's columns
 constexpr int TB_GROUP_STRIDE = 144;       // spacing of the four 128-byte group pieces in a stage
@@ -94,7 +94,8 @@ struct Cfg {
   static constexpr int RING_BYTES = STAGES * X_STAGE_BYTES;
   static constexpr int BARS_OFF = RING_BYTES + W_RING_BYTES;
   static constexpr int SMEM_BYTES = 1024 + BARS_OFF + 512 + 1024 + RECV_BYTES;   // rings, barriers, scale-constant table, receive buffer
-  static constexpr int TMEM_COLS = RP < 32 ? 32 : RP;             // power of two >= 32
+  // Two accumulators: slabs alternate between two issuing warps (see the MMA issuers), each with its own.
+  static constexpr int TMEM_COLS = 2 * (RP < 32 ? 32 : RP);       // power of two >= 64
   static constexpr int EPI_COLS = RP / 4 < 32 ? 32 : RP / 4;      // accumulator columns per epilogue warp
   static_assert(TILE_M * RP * 4 <= RING_BYTES, "partial accumulator must fit in the x ring");
   static_assert(STAGES >= QUANT_GROUPS && STAGES % QUANT_GROUPS == 0, "ring depth");
@@ -172,7 +173,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     *lora_unfit = 0u;
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1 + QUANT_WARPS / QUANT_GROUPS); }
     for (int s = 0; s < C::W_STAGES; ++s) { mbar_init(&wfull[s], 1); mbar_init(&wempty[s], 1); }
-    mbar_init(acc_done, 1);
+    mbar_init(acc_done, my_slabs > 1 ? 2 : 1);     // one arrival per MMA issuer that has slabs
     mbar_init(recv_bar, 1);                    // armed below with the bytes of the peer's two copies
     mbar_init(ack_bar, 1);
     if (kDirectExchange && ks == 2 && has_lora) mbar_arrive_expect_tx(recv_bar, C::RECV_BYTES);
@@ -236,13 +237,20 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         __syncwarp();
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------ MMA issuers ------------------------------
+    // Two warps, even and odd slabs, each into an accumulator of its own (added up in the epilogue, always in
+    // the same order).  One thread's loop - two barrier waits, four MMAs, three commits - takes about 0.3 us
+    // per slab whatever the tensor pipe has to do (it is busy a quarter of the time), which made a single
+    // issuer the slowest agent of the kernel: the x ring ran full behind it and the epilogue started late.
     constexpr uint64_t kDescA = smem_desc_base(0, 1024, kSwizzle128B);               // x tile, K-major
     constexpr uint64_t kDescB = smem_desc_base(SLAB_K * 128, 1024, kSwizzle128B);    // lora_down slab, R-major (its own ring)
     constexpr uint32_t kIdesc = idesc_f16(kBf16, kBf16, TILE_M, RP, false, true);
+    const int issuer = warp >> 1;                                  // 0 or 1
+    const uint32_t acc = tmem_acc + issuer * RP;
+    const int last = ((my_slabs - 1 - issuer) & ~1) + issuer;      // this issuer's last slab (negative: none)
     bool ok = true;
-    for (int i = 0; i < my_slabs && ok; ++i) {
+    for (int i = issuer; i < my_slabs && ok; i += 2) {
       const uint32_t s = i % C::STAGES, ph = (i / C::STAGES) & 1;
       if (!uwait(&full[s], ph, kDevWaitFull, i)) { ok = false; break; }
       const uint32_t sw = i % C::W_STAGES;
@@ -254,10 +262,10 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
         if (has_lora) {
 #pragma unroll
           for (int j = 0; j < SLAB_K / 16; ++j)
-            mma_f16<1>(tmem_acc, smem_desc(kDescA, a_addr + j * 32), smem_desc(kDescB, b_addr + j * 2048), kIdesc,
-                       (i | j) != 0 ? 1u : 0u);
+            mma_f16<1>(acc, smem_desc(kDescA, a_addr + j * 32), smem_desc(kDescB, b_addr + j * 2048), kIdesc,
+                       (i != issuer || j != 0) ? 1u : 0u);
         }
-        if (has_lora) { tc_commit(&empty[s]); tc_commit(&wempty[sw]); if (i == my_slabs - 1) tc_commit(acc_done); }
+        if (has_lora) { tc_commit(&empty[s]); tc_commit(&wempty[sw]); if (i == last) tc_commit(acc_done); }
         else mbar_arrive(&empty[s]);
       }
       __syncwarp();
@@ -326,6 +334,21 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
     asm volatile("bar.sync 2, %0;" ::"n"(QUANT_WARPS * 32) : "memory");
   }
 
+  // 32 accumulator columns of this warp's lanes: the even slabs' accumulator plus, if there is more than one
+  // slab, the odd slabs' (always in this order)
+  auto acc_ld = [&](uint32_t taddr, uint32_t (&v)[32]) {
+    tmem_ld_32x32(taddr, v);
+    if (my_slabs > 1) {
+      uint32_t w[32];
+      tmem_ld_32x32(taddr + RP, w);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __uint_as_float(w[j])));
+    } else {
+      tmem_ld_wait();
+    }
+  };
+
   // ------------------------------ LoRA epilogue ------------------------------
   // The 64 accumulator rows live in lanes 0-15 of each 32-lane quarter of tensor memory:
   // row r is lane (r % 16) + 32 * (r / 16).
@@ -353,8 +376,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 #pragma unroll 1
       for (int c0 = 0; c0 < RP; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(taddr + c0, v);
-        tmem_ld_wait();
+        acc_ld(taddr + c0, v);
         if (lane < 16) {
 #pragma unroll
           for (int j = 0; j < 8; ++j)
@@ -415,8 +437,7 @@ quantize_fused_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_cons
 #pragma unroll 1
         for (int c0 = cpart * C::EPI_COLS; c0 < (cpart + 1) * C::EPI_COLS; c0 += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
-          tmem_ld_wait();
+          acc_ld(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
           if (lane < 16) {
             if (ks > 1) {
 #pragma unroll
