@@ -242,13 +242,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint8_t* tail = store_bufs + C::STORE_BYTES;
   float* affine = reinterpret_cast<float*>(tail);                 // [3 or 4][BN] : wcscales, bias, -smooth_next, 1/smooth_next of the current tile
   uint64_t* bars = reinterpret_cast<uint64_t*>(tail + C::AFFINE_BYTES);
-  uint64_t* full = bars;                                          // [STAGES]     A / B (or LoRA) operands landed (leader CTA's copy is used)
+  uint64_t* full = bars;                                          // [STAGES]     A / B (or LoRA) operands landed and scales copied (leader CTA's copy is used)
   uint64_t* empty = bars + C::STAGES;                             // [STAGES]     stage consumed by the MMAs (per CTA)
   uint64_t* full_sf = bars + 2 * C::STAGES;                       // [STAGES]     the stage's scale atoms landed (leader's copy)
   uint64_t* acc_full = bars + 3 * C::STAGES;                      // [ACC_STAGES] accumulator complete (per CTA)
   uint64_t* acc_empty = acc_full + C::ACC_STAGES;                 // [ACC_STAGES] accumulator drained (leader's copy is used)
-  uint64_t* sf_full = acc_empty + C::ACC_STAGES;                  // [SF_BUFS] scale buffer copied (leader CTA)
-  uint64_t* sf_empty = sf_full + C::SF_BUFS;                      // [SF_BUFS] scale buffer consumed by the MMAs (leader CTA)
+  uint64_t* sf_empty = acc_empty + C::ACC_STAGES;                 // [SF_BUFS] scale buffer consumed by the MMAs (leader CTA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sf_empty + C::SF_BUFS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile uint32_t* sk_ticket = tmem_slot + 2;                   // split-K: the ticket this CTA drew for its tile
@@ -269,9 +268,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&full_sf[s], 1); }
+    // full[s]: the producer's arrival (with the operand bytes) and one arrival per scale copier, made when the
+    // stage's scales are in tensor memory (at once for a LoRA slab): the MMA issuer waits once per slab
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1 + SF_WARPS); mbar_init(&empty[s], 1); mbar_init(&full_sf[s], 1); }
     for (int a = 0; a < C::ACC_STAGES; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], EPI_WARPS * CG); }
-    for (int b = 0; b < C::SF_BUFS; ++b) { mbar_init(&sf_full[b], SF_WARPS); mbar_init(&sf_empty[b], 1); }
+    for (int b = 0; b < C::SF_BUFS; ++b) mbar_init(&sf_empty[b], 1);
     fence_barrier_init();
   }
   if (warp == EPI_WARPS && lane == 0) {
@@ -429,10 +430,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
           if (!uwait(&full[s], ph, ctx, kDevWaitFull, it)) { ok = false; break; }
           const bool main_slab = kt < kt_main;
-          const uint32_t sb = sf_it % C::SF_BUFS;
-          if (main_slab) {
-            if (!uwait(&sf_full[sb], (sf_it / C::SF_BUFS) & 1, ctx, kDevWaitMisc, it)) { ok = false; break; }
-          }
+          const uint32_t sb = sf_it % C::SF_BUFS;            // its scales are in tensor memory: the copiers arrived on full[s]
           tc_fence_after_sync();
           const uint32_t a_addr = smem_u32(smem + s * C::STAGE_BYTES);
           const uint32_t b_addr = a_addr + A_BYTES;
@@ -484,7 +482,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           // parity of a barrier no longer tells the revolutions apart.
           const uint32_t s = it % C::STAGES, ph = (it / C::STAGES) & 1;
           if (!uwait(&full_sf[s], ph, ctx, kDevWaitFull, 0x20000 + it)) { ok = false; break; }
-          if (kt >= kt_main) continue;
+          if (kt >= kt_main) {                               // no scales: this copier's arrival on the stage's barrier at once
+            if (elect_one()) mbar_arrive(&full[s]);
+            __syncwarp();
+            continue;
+          }
           const uint32_t sb = sf_it % C::SF_BUFS;
           if (!uwait(&sf_empty[sb], ((sf_it / C::SF_BUFS) & 1) ^ 1, ctx, kDevWaitMisc, 0x20000 + it)) { ok = false; break; }
           tc_fence_after_sync();
@@ -503,7 +505,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                   tmem_cp_scales<CG>(tsfb + j * (BN / 32) + h * 4, smem_desc(kDescSF, sfb_addr + h * 2048 + j * 512));
               }
             }
-            tc_commit_local<CG>(&sf_full[sb]);
+            tc_commit_local<CG>(&full[s]);                   // arrives once these copies are done
           }
           __syncwarp();
           ++sf_it;
@@ -555,11 +557,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       // Drain: every column this warp owns goes to registers in one burst, the accumulator is handed
       // back at once, and only then do the affine, the packing and the stores happen.
       uint32_t v[C::GROUPS_PER_WARP][2][32];
-#pragma unroll
-      for (int g = 0; g < C::GROUPS_PER_WARP; ++g) {
-        tmem_ld_32x32(taddr + g * 64, v[g][0]);
-        tmem_ld_32x32(taddr + g * 64 + 32, v[g][1]);
-      }
+      if constexpr (C::GROUPS_PER_WARP == 2) tmem_ld_32x32_x128(taddr, &v[0][0][0]);
+      else tmem_ld_32x32_x64(taddr, &v[0][0][0]);
       tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
