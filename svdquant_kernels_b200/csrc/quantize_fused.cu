@@ -8,15 +8,17 @@
 // follow baseline/kernels/quantize_w4a4_act_fuse_lora/ref.py:19-50.
 //
 // Decomposition.  A cluster of KS (1, 2, 4 or 8) CTAs owns one tile of 64 rows; CTA k
-// owns a contiguous range of 64-column slabs of K.  Per slab the producer warp
-// TMA-loads the x tile (64 x 64, 128-byte swizzle) and the matching lora_down
-// slab (64 x R) into one ring stage, together with the slab's 64 entries of
-// the {smooth, 1/smooth} table (a 512-byte bulk copy).
-// Two consumers read the stage: the MMA warp accumulates x_tile @ lora_down_slab
-// into a [64 x R] fp32 accumulator in tensor memory, and sixteen quantize warps
-// turn the tile into codes and scales.  x is read from HBM exactly once.  With
-// KS > 1 the partial accumulators are summed in a fixed order through
-// distributed shared memory: no atomics, no zero-fill, no scratch in global
+// owns a contiguous range of 64-column slabs of K.  Per slab one producer warp
+// TMA-loads the x tile (64 x 64, 128-byte swizzle) with the slab's 64 entries of
+// the smoothing table (four 128-byte bulk copies) into a stage of the x ring, a
+// second one the matching lora_down slab (64 x R) into a ring of its own.
+// Two kinds of consumers read an x stage: two MMA-issuing warps (even and odd
+// slabs) accumulate x_tile @ lora_down_slab into [64 x R] fp32 accumulators in
+// tensor memory, one each, and sixteen quantize warps turn the tile into codes
+// and scales.  x is read from HBM exactly once.  With KS > 1 the partial
+// accumulators are summed in a fixed order (two ranks: through the copy engine
+// into the partner's shared memory; more: through distributed shared memory
+// loads): no atomics, no zero-fill, no scratch in global
 // memory.  Large inputs run with KS = 2; clusters of 4 and 8 are for inputs of
 // a few hundred rows, where pairs would leave most SMs idle (256 x 10240:
 // 36.0 -> 12.9 us), and are taken only if all of them are resident at once.  (64-row tiles with pairs, not 128-row tiles with quads: a B200 keeps
