@@ -20,9 +20,12 @@
 // Issuing one tcgen05.cp costs its thread about 30 cycles (measured), and a
 // 256-wide slab needs 12 scale copies next to its 4 MMAs, which together with
 // the waits is more than the 512 cycles the slab's MMAs run for; so the two
-// kinds are issued by different warps and handshake through mbarriers.  All
-// single-lane roles stay converged and elect one lane per instruction, so
-// descriptors and addresses live in uniform registers.
+// kinds are issued by different warps and handshake through mbarriers: each
+// copier's commit is one of the arrivals the stage's "full" barrier waits for
+// (beside the producer's, which carries the operand bytes), so the MMA issuer
+// waits once per slab and finds operands in shared memory and scales in tensor
+// memory.  All single-lane roles stay converged and elect one lane per
+// instruction, so descriptors and addresses live in uniform registers.
 //
 // CG = 1: a CTA computes a 128 x BN tile.
 // CG = 2: two CTAs of a cluster compute a 256 x BN tile with cta_group::2
