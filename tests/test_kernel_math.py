@@ -128,3 +128,53 @@ def test_signed_truncation_carries_the_sign_through_the_rescale():
         neg = (np.trunc(-t) * rj).astype(np.float32)
         assert (neg == -pos).all()
         assert np.signbit(neg[t < 1]).all() and (neg[t < 1] == 0).all()
+
+
+def _round_to_f32(fr):
+    """Correctly rounded (nearest, ties to even) float32 of an exact rational, normal range only."""
+    from fractions import Fraction
+    if fr == 0:
+        return np.float32(0.0)
+    sign = -1 if fr < 0 else 1
+    fr = abs(fr)
+    e = 0
+    while fr >= Fraction(1 << 24):
+        fr /= 2
+        e += 1
+    while fr < Fraction(1 << 23):
+        fr *= 2
+        e -= 1
+    n = fr.numerator // fr.denominator
+    rem = fr - n
+    if rem > Fraction(1, 2) or (rem == Fraction(1, 2) and (n & 1)):
+        n += 1
+    return np.float32(sign * float(n) * 2.0 ** e)        # n < 2^24 + 1 and a power of two: exact
+
+
+def test_division_through_the_rounded_reciprocal_equals_ieee_division_on_samples():
+    """The next-layer epilogue's divide: q0 = RN(a r), e = a - s q0 (one fma, exact), q = RN(q0 + e r) with
+    r = RN(1 / s), for fp32 dividends and divisors of at most 11 significant bits, against the correctly
+    rounded quotient worked out with rationals.  (The library's device self-test does all 2^23 x 2^10
+    significand pairs; this is the same statement on a sample, for boxes without a GPU.)"""
+    from fractions import Fraction
+    rng = np.random.default_rng(5)
+    # divisors: every 64th 11-bit significand plus the extremes, over a few binades; dividends: random fp32
+    sig = sorted(set(list(range(1024, 2048, 64)) + [1024, 1025, 2046, 2047]))
+    divisors = [np.float32(m * 2.0 ** (k - 10)) for m in sig for k in (-12, -1, 0, 3, 14)]
+    bad = 0
+    checked = 0
+    for s in divisors:
+        r = np.float32(1.0) / s                                  # numpy divides correctly rounded
+        a = (rng.standard_normal(40).astype(np.float32) * np.float32(2.0) ** rng.integers(-20, 20, 40)).astype(np.float32)
+        a[:4] = [np.float32(1.0), np.float32(-3.0), np.nextafter(np.float32(1.0), np.float32(2.0)), s]
+        for av in a:
+            fa, fs, fr = Fraction(float(av)), Fraction(float(s)), Fraction(float(r))
+            q0 = np.float32(av * r)
+            fe = fa - fs * Fraction(float(q0))                    # the fma's exact value ...
+            e = _round_to_f32(fe)
+            assert Fraction(float(e)) == fe, "... which fp32 holds exactly"
+            q = _round_to_f32(Fraction(float(q0)) + fe * fr)
+            want = _round_to_f32(fa / fs)
+            bad += int(q != want)
+            checked += 1
+    assert checked > 3000 and bad == 0
